@@ -4,8 +4,9 @@ from .registry import (ArchitectureEntry, UnknownArchitecture, lookup_architectu
 from .qwen2 import ConfigError, Qwen2Config
 from .vunovik import VunovikConfig
 from .gisirax import GisiraxConfig
+from .lipizen import LipizenConfig
 from . import shapes
 
 __all__ = ["BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec",
            "ArchitectureEntry", "UnknownArchitecture", "lookup_architecture", "read_config_json",
-           "register_architecture", "registered_architectures", "ConfigError", "Qwen2Config", "VunovikConfig", "GisiraxConfig", "ShortConvSpec", "BigramSpec"]
+           "register_architecture", "registered_architectures", "ConfigError", "Qwen2Config", "VunovikConfig", "GisiraxConfig", "LipizenConfig", "ShortConvSpec", "BigramSpec"]

@@ -19,6 +19,7 @@ from typing import Any, Dict, List, Optional, Tuple
 @dataclass(frozen=True)
 class NormSpec:
     kind: str                    # "rmsnorm" | "dyt" (tanh(alpha x) * w + b: no row statistics, eps unused)
+                                 # | "group_rmsnorm" (params["groups"] equal parts of a row, each divided by its own root mean square)
     size: int
     eps: float
     params: Dict[str, Any] = field(default_factory=dict)
@@ -30,7 +31,8 @@ class PositionSpec:
     head_dim: int
     rotary_dim: int              # how many leading dims of a head rotate (<= head_dim, even)
     theta: float
-    # "scaling": {"factor", "low", "high", "original"}: frequencies rescaled by their wavelength (see parts/position.py)
+    # "scaling": {"factor", "low", "high", "original"}: frequencies rescaled by their wavelength (see parts/position.py);
+    # "linear": a factor every frequency is divided by
     params: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -59,7 +61,7 @@ class FeedForwardSpec:
     kind: str                    # "gated_mlp"
     hidden: int
     intermediate: int
-    activation: str              # "silu"
+    activation: str              # "silu"; "swish_clamped" takes params["limit"]
     bias: bool = False
     params: Dict[str, Any] = field(default_factory=dict)
 
@@ -88,6 +90,7 @@ class BlockSpec:
     kind: str                    # "prenorm": x += mixer(norm(x)); x += ffn(norm(x))
                                  # "parallel": h = norm(x); x += mixer(conv(h)) + ffn(h)
                                  # "sandwich": x += m * post(mixer(norm(x))); x += m * post(ffn(norm(x)))
+                                 # "postnorm": x = norm(a x + mixer(x)); x = norm(a x + ffn(x)), a = stream_mult
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]      # None: the layer has no feed-forward ("parallel" only)
     mixer_norm: NormSpec
@@ -103,6 +106,8 @@ class BlockSpec:
     mixer_post_norm: Optional[NormSpec] = None
     ffn_post_norm: Optional[NormSpec] = None
     residual_mult: float = 1.0
+    # "postnorm": the factor of the stream in the sum that the norm behind a sublayer reads
+    stream_mult: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -122,6 +127,7 @@ class ModelSpec:
     head_name: str
     embed_scale: float = 1.0
     embed_bigram: Optional[BigramSpec] = None       # a hashed bigram table added to the token embedding
+    logit_softcap: float = 0.0                      # c > 0: logits <- c * tanh(logits / c)
     # A checkpoint of an untied model that stores no head tensor: the table serves as the head
     # (the reference decides so, src/models/transformer.rs:810, and warns, :839-841).
     head_may_be_absent: bool = False

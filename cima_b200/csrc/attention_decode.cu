@@ -15,7 +15,9 @@
 // src/kernels.cu:547-611) and a merge per head (k_attn_reduce, :615-639).
 //
 // Accepts head_dim in {16, 32, ..., 128}, page_size 64, any group size (16 heads per m-tile), any
-// window; other sizes are refused with a sentence and the caller takes the plain kernel.
+// window; other sizes are refused with a sentence and the caller takes the plain kernel.  With `keep_first` f > 0 the
+// first f positions stay visible below the window: their pages head the list of pages that the splits share.
+// `v_group` neighbouring key heads share one value head (value head = key head / v_group).
 #include "common.cuh"
 
 namespace {
@@ -69,9 +71,10 @@ __host__ __device__ constexpr int decode_stages(int hd, int planes = 2) {
 }
 
 // The splits that get pages of a sequence with ``len`` positions: at most one per page of the visible keys.
-__device__ __forceinline__ int live_splits(int len, int window, int n_splits) {
+__device__ __forceinline__ int live_splits(int len, int window, int keep_first, int n_splits) {
   const int lo = (window > 0 && len > window) ? len - window : 0;
-  return min(n_splits, (len - 1) / PS - lo / PS + 1);
+  const int kept = min((keep_first + PS - 1) / PS, lo / PS);       // pages of kept first positions below the window's
+  return min(n_splits, kept + (len - 1) / PS - lo / PS + 1);
 }
 
 // early: the sequence's lengths, slots and block table, and every page before the one that holds the newest
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfloat16* __restrict__ cache,
                    CimaPaged pg, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int ldo,
-                   int nh, int nkv, int mtiles, float scale, int window, int n_splits, int early, float sink) {
+                   int nh, int nkv, int mtiles, float scale, int window, int n_splits, int early, float sink, int keep_first, int v_group) {
   if (!early) cima_pdl_wait();
   constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
   constexpr int TILE = PS * ROW;                      // elements of one K or V tile
@@ -105,17 +108,20 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   const int slot = seq_slot[b];
   const int lo = (window > 0 && len > window) ? len - window : 0;
   const int pf = lo / PS, pl = (len - 1) / PS;
-  const int npages = pl - pf + 1;
+  const int nkp = min((keep_first + PS - 1) / PS, pf);      // pages of kept first positions below the window's
+  const int npages = nkp + pl - pf + 1;                     // the list: pages 0 .. nkp - 1, then pf .. pl
+  const int vh = kvh / v_group;
   // The pages are shared evenly among S = min(n_splits, pages) splits: split s takes pages [s n / S, (s + 1) n / S).
   // A launch sized for a long context (a captured step keeps its grid while the sequences grow) leaves the
   // blocks beyond S without work; the merge reads the first S partial results only (live_splits there).
-  const int S = live_splits(len, window, n_splits);
+  const int S = live_splits(len, window, keep_first, n_splits);
   if (split >= S) return;
-  const int p0 = pf + (int)((long long)split * npages / S);
-  const int p1 = pf + (int)((long long)(split + 1) * npages / S);
+  const int p0 = (int)((long long)split * npages / S);          // places in the list
+  const int p1 = (int)((long long)(split + 1) * npages / S);
+  auto listed = [&](int i) -> int { return i < nkp ? i : pf + (i - nkp); };
 
-  auto page_of = [&](int page_index) -> int {
-    int e = page_index;
+  auto page_of = [&](int list_index) -> int {
+    int e = listed(list_index);
     if (pg.ring) e %= pg.ring;
     return pg.table[(size_t)slot * pg.width + e];
   };
@@ -123,13 +129,13 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     // one page: K then V, each [PS][HD] contiguous in the cache -> padded rows in shared memory
     // (with one plane the page's vectors are keys and values at once: one copy, and the V tile is the K tile)
     const __nv_bfloat16* src = cache + (((size_t)page * PLANES) * pg.kv_heads + kvh) * (size_t)(PS * HD);
-    const size_t vofs = (size_t)pg.kv_heads * PS * HD;
+    const __nv_bfloat16* vsrc = cache + (((size_t)page * PLANES + 1) * pg.kv_heads + vh) * (size_t)(PS * HD);
     __nv_bfloat16* dst = tiles + (size_t)stage * PLANES * TILE;
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
     for (int c = threadIdx.x; c < PS * CPR; c += WARPS * 32) {
       const int r = c / CPR, cc = c % CPR;
       cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
-      if (PLANES == 2) cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+      if (PLANES == 2) cp_async16(dst + TILE + r * ROW + cc * 8, vsrc + r * HD + cc * 8);
     }
   };
 
@@ -137,7 +143,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   // count the same for every block).
   int ahead = 0;                                      // groups committed so far
   if (early) {
-    while (ahead < STAGES - 1 && p0 + ahead < p1 && p0 + ahead < pl) {
+    while (ahead < STAGES - 1 && p0 + ahead < p1 && listed(p0 + ahead) < pl) {
       issue(page_of(p0 + ahead), ahead);
       cp_async_commit();
       ahead++;
@@ -194,14 +200,14 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
       mma_bf16(s[1], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[2], kb[3]);
     }
     // scale, mask what lies outside [lo, len), running softmax per row (rows g and g + 8)
-    const int key0 = p * PS + kw;
+    const int key0 = listed(p) * PS + kw;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < 2; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
         const int key = key0 + j * 8 + 2 * t + (e & 1);
-        const float v = (key >= lo && key < len) ? s[j][e] * sc2 : -INFINITY;
+        const float v = ((key >= lo || key < keep_first) && key < len) ? s[j][e] * sc2 : -INFINITY;
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -297,13 +303,13 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
 // L2 per split: 8 us at 32 splits.)
 __global__ void __launch_bounds__(128)
 k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seq_len,
-                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int window, int splits_launched, float sink) {
+                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int window, int splits_launched, float sink, int keep_first) {
   cima_pdl_wait();
   __shared__ float w[MAX_SPLITS];
   __shared__ float s_inv;
   const int b = blockIdx.y, h = blockIdx.x;
   const size_t base = ((size_t)b * nh + h) * splits_launched;
-  const int n_splits = live_splits(seq_len[b], window, splits_launched);
+  const int n_splits = live_splits(seq_len[b], window, keep_first, splits_launched);
   if (threadIdx.x < 32) {
     float m[MAX_SPLITS / 32], l[MAX_SPLITS / 32];
     float M = -INFINITY;
@@ -349,7 +355,7 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
 template <int HD, int PLANES>
 int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, const int* seq_slot, const int* seq_len,
                   float* part_o, float* part_ml, void* out, int ldo, int B, int nh, int nkv, float scale, int window,
-                  int n_splits, int early, float sink, cudaStream_t stream) {
+                  int n_splits, int early, float sink, int keep_first, int v_group, cudaStream_t stream) {
   auto kern = k_attention_decode<HD, PLANES>;
   constexpr int STAGES = decode_stages(HD, PLANES);
   const size_t tiles = (size_t)STAGES * PLANES * PS * (HD + 8) * sizeof(__nv_bfloat16);
@@ -365,10 +371,10 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
   dim3 grid(n_splits, nkv * mtiles, B);
   { int rc_ = cima_launch(kern, dim3(grid), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, (const __nv_bfloat16*)cache, pg, seq_slot,
                                            seq_len, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, nkv, mtiles, scale,
-                                           window, n_splits, early, sink); if (rc_) return rc_; }
+                                           window, n_splits, early, sink, keep_first, v_group); if (rc_) return rc_; }
   int rc = cima_launch_result();
   if (rc || n_splits == 1) return rc;
-  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, seq_len, (__nv_bfloat16*)out, ldo, nh, HD, window, n_splits, sink); if (rc_) return rc_; }
+  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, seq_len, (__nv_bfloat16*)out, ldo, nh, HD, window, n_splits, sink, keep_first); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
@@ -382,18 +388,19 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
 extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, float* part_o,
                                      float* part_ml, void* out, int ldo, int B, int nh, int nkv, int hd, float scale,
-                                     int window, int n_splits, int early, int planes, float sink, cudaStream_t stream) {
+                                     int window, int n_splits, int early, int planes, float sink, int keep_first, int v_group, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_decode: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (page_size != PS) return cima_fail(CIMA_E_SIZE, "attention_decode: page size %d; this kernel takes 64", page_size);
   if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d; this kernel takes multiples of 16 up to 128", hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
+  if (keep_first < 0 || v_group < 1 || nkv % v_group || (v_group > 1 && planes != 2)) return cima_fail(CIMA_E_ARG, "attention_decode: keep_first %d must not be negative and %d kv heads (two planes) be a multiple of v_group %d", keep_first, nkv, v_group);
   if (n_splits < 1 || n_splits > MAX_SPLITS || B > 65535) return cima_fail(CIMA_E_SIZE, "attention_decode: %d splits / %d sequences exceed one launch", n_splits, B);
   if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
   if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
-#define CASE(H) case H: return planes == 2 ? launch_decode<H, 2>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, stream) \
-                                          : launch_decode<H, 1>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, stream)
+#define CASE(H) case H: return planes == 2 ? launch_decode<H, 2>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, keep_first, v_group, stream) \
+                                          : launch_decode<H, 1>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, keep_first, v_group, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }
@@ -448,5 +455,5 @@ extern "C" int cima_attention_decode_static(const void* qkv, int ld, const void*
   float* part_o = scratch;                       // [B, nh, n_splits, hd]
   float* part_ml = scratch + cells * hd;         // [B, nh, n_splits, 2]
   return cima_attention_decode(qkv, ld, cache, table, table_width, ring, page_size, seq_slot, seq_len, part_o, part_ml,
-                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, 2, 0.f, stream);
+                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, 2, 0.f, 0, 1, stream);
 }

@@ -5,7 +5,10 @@
 //           its row j), used for prefill;
 //   cache - the layer's pages through the slot's block table, used for decoding.
 // Head h reads kv head h / (heads / kv_heads); score = q.k * scale; a query at position p sees
-// keys j <= p, and with window w > 0 only p - j < w (src/kernels.cu:458-491, :700-712).
+// keys j <= p, and with window w > 0 only p - j < w (src/kernels.cu:458-491, :700-712); with `keep_first` f > 0 the
+// first f positions stay visible beyond the window (at their own positions).  `v_group` neighbouring key heads share
+// one value head (1: a value head for every key head): value head = key head / v_group, and a row of the step holds
+// nkv / v_group value heads behind its key heads.
 // A row's result depends only on its own sequence: same bits alone or in any batch.
 #include "common.cuh"
 
@@ -14,7 +17,7 @@ __global__ void __launch_bounds__(128)
 k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cache, CimaPaged pg,
                   const int* __restrict__ row_pos, const int* __restrict__ row_seq,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
-                  TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window, float sink) {
+                  TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window, float sink, int keep_first, int v_group) {
   cima_pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -25,7 +28,8 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
   const int seq = row_seq[row];
   const int slot = FROM_CACHE ? seq_slot[seq] : 0;
   const int first = FROM_CACHE ? 0 : seq_first_row[seq];
-  const int kcol = (nh + kvh) * hd, vcol = (nh + nkv + kvh) * hd;
+  const int vh = kvh / v_group;
+  const int kcol = (nh + kvh) * hd, vcol = (nh + nkv + vh) * hd;
 
   float q[NI], acc[NI];
   const TA* qp = qkv + (size_t)row * ld + (size_t)h * hd;
@@ -37,11 +41,13 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
   }
   float m = -1e30f, l = 0.f;
   const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-  for (int j = lo; j <= pos; j++) {
+  const int kept = min(keep_first, lo);         // the first positions that stay visible below the window
+  for (int j = kept > 0 ? 0 : lo; j <= pos; j++) {
+    if (j == kept && j < lo) j = lo;
     const TA *kp, *vp;
     if (FROM_CACHE) {
       kp = cache + pg.offset(slot, j, 0, kvh);
-      vp = cache + pg.offset(slot, j, 1, kvh);
+      vp = cache + pg.offset(slot, j, 1, vh);
     } else {
       kp = qkv + (size_t)(first + j) * ld + kcol;
       vp = qkv + (size_t)(first + j) * ld + vcol;
@@ -80,18 +86,19 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
                                     int table_width, int ring, int page_size, const int* row_pos,
                                     const int* row_seq, const int* seq_slot, const int* seq_first_row, void* out,
                                     int ldo, int T, int nh, int nkv, int hd, float scale, int window,
-                                    int from_cache, int planes, float sink, cudaStream_t stream) {
+                                    int from_cache, int planes, float sink, int keep_first, int v_group, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd > 1024) return cima_fail(CIMA_E_SIZE, "attention_plain: head_dim %d is outside 1..1024", hd);
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_plain: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_plain: %d heads are not a multiple of %d kv heads", nh, nkv);
   if (nh > 65535) return cima_fail(CIMA_E_SIZE, "attention_plain: %d heads exceed one launch", nh);
+  if (keep_first < 0 || v_group < 1 || nkv % v_group) return cima_fail(CIMA_E_ARG, "attention_plain: keep_first %d must not be negative and %d kv heads be a multiple of v_group %d", keep_first, nkv, v_group);
   if (from_cache && (!cache || !table)) return cima_fail(CIMA_E_ARG, "attention_plain: decoding needs the cache and its block table");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
   dim3 grid((T + 3) / 4, nh);
 #define LAUNCH(TA, FC) { int rc_ = hd <= 256 ? LAUNCH_NI(TA, FC, 8) : LAUNCH_NI(TA, FC, 32); if (rc_) return rc_; }
 #define LAUNCH_NI(TA, FC, NI) cima_launch(k_attention_plain<TA, FC, NI>, dim3(grid), dim3(128), (size_t)(0), stream, 1, (const TA*)qkv, ld, (const TA*)cache, pg, \
-    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window, sink)
+    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window, sink, keep_first, v_group)
   if (dtype == CIMA_F32) { if (from_cache) LAUNCH(float, true) else LAUNCH(float, false) }
   else if (dtype == CIMA_BF16) { if (from_cache) LAUNCH(__nv_bfloat16, true) else LAUNCH(__nv_bfloat16, false) }
   else return cima_fail(CIMA_E_DTYPE, "attention_plain: dtype code %d is neither float32 nor bfloat16", dtype);

@@ -11,7 +11,8 @@
 // sums are float32 (exponentials as 2^(s * scale * log2 e - m) by ex2.approx, whose error is far below
 // the bfloat16 rounding of P);
 // P is rounded to bfloat16 only as the operand of P V.  Key tiles wholly above the
-// diagonal or wholly below the window are skipped.  The list of (sequence, first row) of the blocks
+// diagonal or wholly below the window are skipped.  With `keep_first` f > 0 the first f positions stay visible below
+// the window: their tiles are visited first.  `v_group` neighbouring key heads share one value head.  The list of (sequence, first row) of the blocks
 // comes from the host, heaviest first.
 //
 // Counterpart in the reference: k_attn_prefill_tiled (src/kernels.cu:659-753), one warp per query
@@ -64,7 +65,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
                     const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
                     const __nv_bfloat16* __restrict__ cache, CimaPaged pg, const int* __restrict__ seq_slot,
                     const int* __restrict__ seq_len,
-                    __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window, float sink) {
+                    __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window, float sink, int keep_first, int v_group) {
   cima_pdl_wait();
   constexpr int ROW = HD + 8;
   constexpr int TILE = BN * ROW;
@@ -84,7 +85,8 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   const int h = blockIdx.x % nh, kvh = h / (nh / nkv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int kcol = (nh + kvh) * HD, vcol = (nh + nkv + kvh) * HD;
+  const int vh = kvh / v_group;
+  const int kcol = (nh + kvh) * HD, vcol = (nh + nkv + vh) * HD;
   const float sc2 = scale * 1.4426950408889634f;       // scores are kept in the base-2 domain
 
   // this thread's two query rows (among the sequence's rows; their positions are start + row)
@@ -113,6 +115,9 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   const int last_q = min(q0 + BM, len) - 1;
   const int lo_key = (window > 0 && start + q0 + 1 > window) ? start + q0 + 1 - window : 0;
   const int t0 = lo_key / BN, t1 = (start + last_q) / BN + 1;
+  const int nkeep = min((keep_first + BN - 1) / BN, t0);       // tiles of kept first positions that lie below the window's
+  const int n_iter = nkeep + t1 - t0;
+  auto tile_of = [&](int it) { return it < nkeep ? it : t0 + (it - nkeep); };
 
   auto issue = [&](int kt, int stage) {
     __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
@@ -123,11 +128,12 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
       if (pg.ring) e %= pg.ring;
       const int page = pg.table[(size_t)slot * pg.width + e];
       const __nv_bfloat16* src = cache + (((size_t)page * pg.planes) * pg.kv_heads + kvh) * (size_t)(BN * HD);
-      const size_t vofs = pg.planes == 2 ? (size_t)pg.kv_heads * BN * HD : 0;      // one plane: the values are the keys
+      // one plane: the values are the keys
+      const __nv_bfloat16* vsrc = pg.planes == 2 ? cache + (((size_t)page * 2 + 1) * pg.kv_heads + vh) * (size_t)(BN * HD) : src;
       for (int c = threadIdx.x; c < BN * CPR; c += WARPS * 32) {
         const int r = c / CPR, cc = c % CPR;
         cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
-        cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+        cp_async16(dst + TILE + r * ROW + cc * 8, vsrc + r * HD + cc * 8);
       }
     } else {
       for (int c = threadIdx.x; c < BN * CPR; c += WARPS * 32) {
@@ -145,11 +151,12 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
     }
   };
 
-  issue(t0, 0);
+  issue(tile_of(0), 0);
   cp_async_commit();
-  for (int kt = t0; kt < t1; kt++) {
-    const int stage = (kt - t0) & 1;
-    if (kt + 1 < t1) issue(kt + 1, stage ^ 1);
+  for (int it = 0; it < n_iter; it++) {
+    const int kt = tile_of(it);
+    const int stage = it & 1;
+    if (it + 1 < n_iter) issue(tile_of(it + 1), stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -193,7 +200,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
         for (int e = 0; e < 4; e++) {
           const int key = key_base + j * 8 + 2 * t + (e & 1);
           const int qp = start + ((e >> 1) ? r1 : r0);
-          const bool seen = key <= qp && (window <= 0 || qp - key < window);
+          const bool seen = key <= qp && (window <= 0 || qp - key < window || key < keep_first);
           const float v = seen ? s[j][e] * sc2 : -INFINITY;
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -276,7 +283,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
 template <int HD, bool FROM_CACHE>
 int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
                    const void* cache, const CimaPaged& pg, const int* seq_slot, const int* seq_len,
-                   void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window, float sink, cudaStream_t stream) {
+                   void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window, float sink, int keep_first, int v_group, cudaStream_t stream) {
   if ((long long)n_tiles * nh > 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "attention_prefill: %d blocks of rows x %d heads exceed one launch", n_tiles, nh);
   auto kern = k_attention_prefill<HD, FROM_CACHE>;
   const size_t smem = (size_t)2 * 2 * BN * (HD + 8) * sizeof(__nv_bfloat16);
@@ -288,13 +295,14 @@ int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile
   }
   { int rc_ = cima_launch(kern, dim3((unsigned)n_tiles * (unsigned)nh), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
                                                         (const __nv_bfloat16*)cache, pg, seq_slot, seq_len,
-                                                        (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window, sink); if (rc_) return rc_; }
+                                                        (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window, sink, keep_first, v_group); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
 }  // namespace
 
-static int prefill_checks(const char* who, const void* qkv, int ld, const void* out, int ldo, int hd, int nh, int nkv) {
+static int prefill_checks(const char* who, const void* qkv, int ld, const void* out, int ldo, int hd, int nh, int nkv, int keep_first, int v_group) {
+  if (keep_first < 0 || v_group < 1 || nkv % v_group) return cima_fail(CIMA_E_ARG, "%s: keep_first %d must not be negative and %d kv heads be a multiple of v_group %d", who, keep_first, nkv, v_group);
   if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "%s: head_dim %d; this kernel takes multiples of 16 up to 128", who, hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh > 65535) return cima_fail(CIMA_E_SIZE, "%s: %d heads / %d kv heads are not accepted", who, nh, nkv);
   if (ld % 8 || ldo % 2 || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3))
@@ -305,11 +313,11 @@ static int prefill_checks(const char* who, const void* qkv, int ld, const void* 
 // tile_seq / tile_row0 [n_tiles]: the sequence and the first query row of each block of 64 rows.
 extern "C" int cima_attention_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
                                       const int* seq_first_row, void* out, int ldo, int T, int n_tiles, int nh, int nkv,
-                                      int hd, float scale, int window, float sink, cudaStream_t stream) {
+                                      int hd, float scale, int window, float sink, int keep_first, int v_group, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
-  if (int rc = prefill_checks("attention_prefill", qkv, ld, out, ldo, hd, nh, nkv)) return rc;
+  if (int rc = prefill_checks("attention_prefill", qkv, ld, out, ldo, hd, nh, nkv, keep_first, v_group)) return rc;
   const CimaPaged none{nullptr, 0, 0, BN, nkv, hd};
-#define CASE(H) case H: return launch_prefill<H, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, nullptr, none, nullptr, nullptr, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, stream)
+#define CASE(H) case H: return launch_prefill<H, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, nullptr, none, nullptr, nullptr, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, keep_first, v_group, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }
@@ -323,14 +331,14 @@ extern "C" int cima_attention_extend(const void* qkv, int ld, const int* tile_se
                                      const int* seq_first_row, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, void* out, int ldo,
                                      int T, int n_tiles, int nh, int nkv, int hd, float scale, int window,
-                                     int planes, float sink, cudaStream_t stream) {
+                                     int planes, float sink, int keep_first, int v_group, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_extend: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
-  if (int rc = prefill_checks("attention_extend", qkv, ld, out, ldo, hd, nh, nkv)) return rc;
+  if (int rc = prefill_checks("attention_extend", qkv, ld, out, ldo, hd, nh, nkv, keep_first, v_group)) return rc;
   if (page_size != BN) return cima_fail(CIMA_E_SIZE, "attention_extend: page size %d; this kernel takes %d", page_size, BN);
   if (!cache || !table || !seq_slot || !seq_len || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_extend: the cache (16-byte aligned), its block table, slots and lengths are needed");
   const CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
-#define CASE(H) case H: return launch_prefill<H, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, cache, pg, seq_slot, seq_len, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, stream)
+#define CASE(H) case H: return launch_prefill<H, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, cache, pg, seq_slot, seq_len, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, keep_first, v_group, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }

@@ -52,6 +52,19 @@ __device__ __forceinline__ float cima_gate_act(float g, int act) {
   }
 }
 
+// A gated feed-forward's middle, float32: act(g) * u for the activations above, and one more form that clamps first,
+//   g <- min(g, limit), u <- clamp(u, -limit, limit);  g * sigmoid(1.702 g) * (u + 1)
+// (code CIMA_GATED_SWISH_CLAMPED; the kernels that take it take `limit` beside the code).
+enum { CIMA_GATED_SWISH_CLAMPED = 4, CIMA_GATED_COUNT = 5 };
+__device__ __forceinline__ float cima_gated(float g, float u, int act, float limit) {
+  if (act == CIMA_GATED_SWISH_CLAMPED) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return cima_gate_act(g, act) * u;
+}
+
 // Sum over the threads of a block in a fixed order (warp shuffles, then warp 0 over the warps'
 // partial sums), so that a row's result never depends on what else is launched with it.
 // `red` is shared memory of at least 32 floats.  Every thread gets the total.

@@ -149,18 +149,18 @@ extern "C" int cima_rmsnorm(const float* x, const float* w, void* y, int y_dtype
 // gu is [T, 2I] with the gate in columns [0, I) and the up projection in [I, 2I).
 // The bfloat16 kernel moves 16 bytes per access when I is a multiple of 8; otherwise element by element.
 template <typename TA>
-__global__ void k_swiglu(const TA* __restrict__ gu, TA* __restrict__ a, size_t total, int I, int act) {
+__global__ void k_swiglu(const TA* __restrict__ gu, TA* __restrict__ a, size_t total, int I, int act, float limit) {
   cima_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / I;
     const int c = (int)(idx - row * I);
     const float g = cima_to_f32<TA>(gu[row * 2 * I + c]);
     const float u = cima_to_f32<TA>(gu[row * 2 * I + I + c]);
-    a[idx] = cima_from_f32<TA>(cima_gate_act(g, act) * u);
+    a[idx] = cima_from_f32<TA>(cima_gated(g, u, act, limit));
   }
 }
 
-__global__ void k_swiglu_bf16x8(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ a, size_t groups, int I8, int act) {
+__global__ void k_swiglu_bf16x8(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ a, size_t groups, int I8, int act, float limit) {
   cima_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / I8;
@@ -174,26 +174,26 @@ __global__ void k_swiglu_bf16x8(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 #pragma unroll
     for (int e = 0; e < 4; e++) {
       const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
-      op[e] = __floats2bfloat162_rn(cima_gate_act(g.x, act) * u.x, cima_gate_act(g.y, act) * u.y);
+      op[e] = __floats2bfloat162_rn(cima_gated(g.x, u.x, act, limit), cima_gated(g.y, u.y, act, limit));
     }
     *reinterpret_cast<uint4*>(a + idx * 8) = ov;
   }
 }
 
-extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, int act, cudaStream_t stream) {
+extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, int act, float limit, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "swiglu: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
+  if (act < 0 || act >= CIMA_GATED_COUNT) return cima_fail(CIMA_E_ARG, "swiglu: activation code %d is not one of 0..%d", act, CIMA_GATED_COUNT - 1);
   if (I <= 0) return cima_fail(CIMA_E_SIZE, "swiglu: intermediate width %d must be positive", I);
   const size_t total = (size_t)T * I;
   if (dtype == CIMA_BF16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)a) & 15) == 0) {
     const size_t groups = total / 8;
     const int grid = (int)((groups + 255) / 256 > 148 * 16 ? 148 * 16 : (groups + 255) / 256);
-    { int rc_ = cima_launch(k_swiglu_bf16x8, dim3(grid), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, groups, I / 8, act); if (rc_) return rc_; }
+    { int rc_ = cima_launch(k_swiglu_bf16x8, dim3(grid), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, groups, I / 8, act, limit); if (rc_) return rc_; }
     return cima_launch_result();
   }
   const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
-  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_swiglu<float>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const float*)gu, (float*)a, total, I, act); if (rc_) return rc_; }
-  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_swiglu<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I, act); if (rc_) return rc_; }
+  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_swiglu<float>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const float*)gu, (float*)a, total, I, act, limit); if (rc_) return rc_; }
+  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_swiglu<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I, act, limit); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "swiglu: dtype code %d is neither float32 nor bfloat16", dtype);
   return cima_launch_result();
 }
@@ -258,5 +258,21 @@ __global__ void k_decode_advance(const int* __restrict__ chosen, int* __restrict
 extern "C" int cima_decode_advance(const int* chosen, int* tokens, int* row_pos, int* seq_len, int B, cudaStream_t stream) {
   if (B <= 0) return 0;
   { int rc_ = cima_launch(k_decode_advance, dim3((B + 127) / 128), dim3(128), (size_t)(0), stream, 1, chosen, tokens, row_pos, seq_len, B); if (rc_) return rc_; }
+  return cima_launch_result();
+}
+
+// ---------------------------------------------------------------- logits capped softly: z <- cap * tanh(z / cap), in place
+__global__ void k_softcap(float* __restrict__ z, size_t total, float cap) {
+  cima_pdl_wait();
+  const float inv = 1.0f / cap;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    z[idx] = cap * tanhf(z[idx] * inv);
+}
+
+extern "C" int cima_softcap(float* z, size_t total, float cap, cudaStream_t stream) {
+  if (total == 0) return 0;
+  if (!(cap > 0.f)) return cima_fail(CIMA_E_ARG, "softcap: the cap %g must be positive", (double)cap);
+  const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
+  { int rc_ = cima_launch(k_softcap, dim3(grid), dim3(256), (size_t)0, stream, 1, z, total, cap); if (rc_) return rc_; }
   return cima_launch_result();
 }

@@ -2,9 +2,84 @@
 //   group_rmsnorm_gate   out = o / sqrt(mean_group(o^2) + eps) * w * sigmoid(gate)      per group of n values of a row
 //                        (a group = a head's values with one shared weight [n], or the whole row with a weight [G n])
 //   rms_mean             x += (1 / B) * sum_b  y_b / sqrt(mean(y_b^2) + eps) * w_b        B <= 4 branches of one width
+//   scale_add_group_rmsnorm   x <- N(alpha x + y), N the norm in groups with weight w [G n]; also h = x in another dtype
+//                        (the norm behind a sublayer's sum: the stream, the sum and the norm in one pass)
 #include "common.cuh"
 
 namespace {
+// A warp a (row, group) of at most 1,024 values (32 a lane, kept in registers between the two passes).
+template <typename TH>
+__global__ void __launch_bounds__(128)
+k_scale_add_group_rmsnorm(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ w,
+                          TH* __restrict__ h, long long units, int groups, int n, float eps) {
+  cima_pdl_wait();
+  cima_pdl_trigger();
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= units) return;
+  const int lane = threadIdx.x & 31;
+  const int grp = (int)(unit % groups);
+  const size_t base = (size_t)unit * n;
+  float v[32];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    const int i = lane + 32 * j;
+    v[j] = 0.f;
+    if (i < n) {
+      v[j] = y ? fmaf(alpha, x[base + i], y[base + i]) : alpha * x[base + i];
+      ss = fmaf(v[j], v[j], ss);
+    }
+  }
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float r = 1.0f / sqrtf(ss / (float)n + eps);
+  const float* wp = w + (size_t)grp * n;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    const int i = lane + 32 * j;
+    if (i < n) {
+      const float o = v[j] * r * wp[i];
+      x[base + i] = o;
+      if (h) h[base + i] = cima_from_f32<TH>(o);
+    }
+  }
+}
+
+// Longer groups: a block a (row, group), the sum read twice.
+template <typename TH>
+__global__ void __launch_bounds__(256)
+k_scale_add_group_rmsnorm_wide(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ w,
+                               TH* __restrict__ h, int groups, int n, float eps) {
+  cima_pdl_wait();
+  cima_pdl_trigger();
+  __shared__ float red[32];
+  const long long unit = blockIdx.x;
+  const int grp = (int)(unit % groups);
+  const size_t base = (size_t)unit * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = y ? fmaf(alpha, x[base + i], y[base + i]) : alpha * x[base + i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = cima_block_sum(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)n + eps);
+  const float* wp = w + (size_t)grp * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = y ? fmaf(alpha, x[base + i], y[base + i]) : alpha * x[base + i];
+    const float o = v * r * wp[i];
+    x[base + i] = o;
+    if (h) h[base + i] = cima_from_f32<TH>(o);
+  }
+}
+
+template <typename TH>
+__global__ void __launch_bounds__(256)
+k_cast_rows(const float* __restrict__ x, TH* __restrict__ h, size_t total) {
+  cima_pdl_wait();
+  cima_pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) h[i] = cima_from_f32<TH>(x[i]);
+}
+
 template <typename TG, typename TO>
 __global__ void __launch_bounds__(128)
 k_group_rmsnorm_gate(const float* __restrict__ o, const float* __restrict__ w, const TG* __restrict__ gate, int ldg,
@@ -111,5 +186,38 @@ extern "C" int cima_rms_mean(const float* const* ys, const float* const* ws, int
   br.n = n_branches;
   for (int b = 0; b < n_branches; b++) { br.y[b] = ys[b]; br.w[b] = ws[b]; }
   int rc = cima_launch(k_rms_mean, dim3(T), dim3(256), (size_t)0, stream, 1, br, x, H, eps, assign);
+  return rc ? rc : cima_launch_result();
+}
+
+// x [T, groups * n] float32 becomes N(alpha x + y) (y float32 of the same shape, or null for N(alpha x)); w [groups * n];
+// h (hdtype, may be null) receives the same rows in that dtype.
+extern "C" int cima_scale_add_group_rmsnorm(float* x, const float* y, float alpha, const float* w, void* h, int hdtype, int T,
+                                            int groups, int n, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (groups <= 0 || n <= 0) return cima_fail(CIMA_E_SIZE, "scale_add_group_rmsnorm: %d groups of %d values must be positive", groups, n);
+  if (h && hdtype != CIMA_F32 && hdtype != CIMA_BF16) return cima_fail(CIMA_E_DTYPE, "scale_add_group_rmsnorm: dtype code %d is neither float32 nor bfloat16", hdtype);
+  const long long units = (long long)T * groups;
+  if (units >= 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "scale_add_group_rmsnorm: %d rows x %d groups exceed one launch", T, groups);
+  int rc;
+  if (n <= 1024) {
+    const dim3 grid((unsigned)((units + 3) / 4));
+    if (h && hdtype == CIMA_BF16) rc = cima_launch(k_scale_add_group_rmsnorm<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream, 1, x, y, alpha, w, (__nv_bfloat16*)h, units, groups, n, eps);
+    else rc = cima_launch(k_scale_add_group_rmsnorm<float>, grid, dim3(128), (size_t)0, stream, 1, x, y, alpha, w, (float*)h, units, groups, n, eps);
+  } else {
+    if (h && hdtype == CIMA_BF16) rc = cima_launch(k_scale_add_group_rmsnorm_wide<__nv_bfloat16>, dim3((unsigned)units), dim3(256), (size_t)0, stream, 1, x, y, alpha, w, (__nv_bfloat16*)h, groups, n, eps);
+    else rc = cima_launch(k_scale_add_group_rmsnorm_wide<float>, dim3((unsigned)units), dim3(256), (size_t)0, stream, 1, x, y, alpha, w, (float*)h, groups, n, eps);
+  }
+  return rc ? rc : cima_launch_result();
+}
+
+// h = x in another dtype (the rows a sublayer reads where no norm stands in front of it).
+extern "C" int cima_cast_rows(const float* x, void* h, int hdtype, size_t total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const size_t blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffull) return cima_fail(CIMA_E_SIZE, "cast_rows: %zu values exceed one launch", total);
+  int rc;
+  if (hdtype == CIMA_BF16) rc = cima_launch(k_cast_rows<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, 1, x, (__nv_bfloat16*)h, total);
+  else if (hdtype == CIMA_F32) rc = cima_launch(k_cast_rows<float>, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, 1, x, (float*)h, total);
+  else return cima_fail(CIMA_E_DTYPE, "cast_rows: dtype code %d is neither float32 nor bfloat16", hdtype);
   return rc ? rc : cima_launch_result();
 }

@@ -69,9 +69,10 @@ struct PairArgs {
   void* out;                  // out[i * ldo + j]
   int ldo;
   int* error_flag;
-  int act;                    // gated epilogue: the gate's activation (CIMA_ACT_*)
+  int act;                    // gated epilogue: the gate's activation (CIMA_ACT_*, or CIMA_GATED_SWISH_CLAMPED with its limit)
   const int* tile_expert;     // grouped: [p_tiles] which matrix of Q a row tile multiplies with (-1: none), else null
   int q_stride;               // grouped: rows of Q from one matrix to the next
+  float act_limit = 0.f;      // the limit of CIMA_GATED_SWISH_CLAMPED
 };
 
 // The rows a tile loads: its own 256, but the last tile of a matrix of at least 256 rows starts early enough to end
@@ -197,7 +198,7 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           float u[32];
           tmem_ld32(acc + (unsigned)(BN / 2 + c0), u);
 #pragma unroll
-          for (int e = 0; e < 32; e++) v[e] = (a.act == CIMA_ACT_SILU ? v[e] / (1.0f + expf(-v[e])) : cima_gate_act(v[e], a.act)) * u[e];
+          for (int e = 0; e < 32; e++) v[e] = a.act == CIMA_ACT_SILU ? v[e] / (1.0f + expf(-v[e])) * u[e] : cima_gated(v[e], u[e], a.act, a.act_limit);
         }
         if (i >= p_first && i < a.p_rows) {
           const int jmax = GATED ? a.up_offset : a.q_rows;
@@ -290,9 +291,9 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const PairArgs& a, int 
 // out[i, j] = epilogue(sum_k P[i, k] Q[j, k]); P [p_rows, K], Q [q_rows, K] bf16, 16-byte aligned, K % 8 == 0.
 // Tiles of 256 rows x 256 columns per pair of SMs.  Epilogues: 0 store bf16 (+ bias), 1 accumulate into float32, 2 act(gate) * up (Q = [gate | up]; act: CIMA_ACT_*), 3 store float32.
 extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float* bias, void* out, int epi, int p_rows,
-                                      int q_rows, int K, int ldo, int up_offset, int act, int* error_flag, cudaStream_t stream) {
+                                      int q_rows, int K, int ldo, int up_offset, int act, float act_limit, int* error_flag, cudaStream_t stream) {
   if (p_rows <= 0 || q_rows <= 0) return 0;
-  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
+  if (act < 0 || act >= CIMA_GATED_COUNT) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: activation code %d is not one of 0..%d", act, CIMA_GATED_COUNT - 1);
   if (K <= 0 || K % 8) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair: K %d must be a positive multiple of 8", K);
   if (((uintptr_t)P | (uintptr_t)Q) & 15) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: P and Q must be 16-byte aligned");
   if (!error_flag) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: an error flag on the device is needed");
@@ -308,7 +309,7 @@ extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float*
   if (rc) return rc;
   rc = make_map(&mq, Q, q_rows, K, K, BN / 2);
   if (rc) return rc;
-  PairArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, error_flag, act, nullptr, 0};
+  PairArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, error_flag, act, nullptr, 0, act_limit};
   switch (epi) {
     case EPI_STORE: return launch<BN, 6, EPI_STORE>(mp, mq, a, p_tiles, tiles_q, stream);
     case EPI_ACCUM: return launch<BN, 6, EPI_ACCUM>(mp, mq, a, p_tiles, tiles_q, stream);

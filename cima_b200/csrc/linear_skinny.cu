@@ -74,7 +74,8 @@ struct SkinnyNorm {
   float* ssq_out;        // [M, tiles] or null (accumulating epilogue only)
   const float* w_next;   // [N] weight of the norm that follows, with xw_out; both null = not wanted
   __nv_bfloat16* xw_out;
-  int act;               // gated epilogue: the gate's activation (CIMA_ACT_*)
+  int act;               // gated epilogue: the gate's activation (CIMA_ACT_*, or CIMA_GATED_SWISH_CLAMPED with its limit)
+  float act_limit;
 };
 
 // Mode 4: the q/k/v projection of a decode step with the rotary encoding and the append to the cache in its
@@ -306,7 +307,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
         ((float*)out)[o] = v[0] + (bias ? bias[n] : 0.f);
       } else {
         const float gate = v[0], up = v[MT - 1];
-        ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(cima_gate_act(gate, nm.act) * up);
+        ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(cima_gated(gate, up, nm.act, nm.act_limit));
       }
     }
   }
@@ -384,15 +385,15 @@ static int skinny_checks(const void* X, const void* W, const float* bias, int mo
 // w_next / xw_out (mode 1 with ssq_out, may be null): weight [N] of the norm that follows, and where to put
 // bf16(updated row * that weight), [M, N] with row stride ldo.
 extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
-                                  int K, int ldx, int ldo, float* ssq_out, const float* w_next, void* xw_out, int act,
+                                  int K, int ldx, int ldo, float* ssq_out, const float* w_next, void* xw_out, int act, float act_limit,
                                   cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "linear_skinny: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
+  if (act < 0 || act >= CIMA_GATED_COUNT) return cima_fail(CIMA_E_ARG, "linear_skinny: activation code %d is not one of 0..%d", act, CIMA_GATED_COUNT - 1);
   int rc = skinny_checks(X, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
   if (xw_out && (mode != SK_ACCUM || !ssq_out || !w_next)) return cima_fail(CIMA_E_ARG, "linear_skinny: the scaled rows go with mode 1, the partial sums and the next norm's weight");
   SkinnyNorm nm{nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr,
-                mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr, act};
+                mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr, act, act_limit};
   return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
@@ -408,7 +409,7 @@ extern "C" int cima_linear_skinny_norm(const void* xw, const float* ssq, int par
   if (mode == SK_ACCUM) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the accumulating epilogue reads activations, not the residual");
   int rc = skinny_checks(xw, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
-  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr, act};
+  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr, act, 0.f};
   return dispatch_mode<1, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 

@@ -4,6 +4,9 @@
 //   decay rule   S <- d_h S + k v^T;                       o = S^T q       d_h one constant a head; q, k, v through SiLU
 //   delta rule   S <- diag(g_t) S;  u = beta_t (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                g_t one decay a key channel and token, beta_t one scalar a token; the read-out sees the token's write
+//   gate rule    S <- diag(f_t) S + (1 - f_t) v^T;          o = S^T q       f_t = l + (1 - l) sigmoid(z_t + b) one forget gate
+//                a key channel and token, made here from the projection z, a bias b and a lower bound l (both
+//                [heads * dim]); what the gate forgets is what it lets in; q through SiLU, v as it is
 //
 // A block owns 32 neighbouring value channels (columns of S) of one (sequence, head); a column is shared by 8 lanes of a
 // warp, each of which keeps an eighth of the column's rows in registers (rows 32 ii + 4 rg + e of row group rg, so that the
@@ -32,19 +35,21 @@ __device__ __forceinline__ float rec_sum_over_lanes(float v) {        // over th
 // CPT: columns a thread owns (its columns stand 32 apart).  With two, every read of k, q and g from shared memory serves
 // both, but a block covers 64 columns and a sequence gets half as many blocks: measured slower for one prompt (1.2 ms
 // against 0.97 ms a layer of 2,048 tokens at key and value size 128), so the launch takes one.
-template <typename TQ, typename TV, int DIMP, bool DELTA, int CPT>
+// MODE: 0 the decay rule, 1 the delta rule, 2 the gate rule.
+template <typename TQ, typename TV, int DIMP, int MODE, int CPT>
 __global__ void __launch_bounds__(REC_THREADS)
 k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
              const float* __restrict__ g, const float* __restrict__ beta, const float* __restrict__ decay,
              float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
              float* __restrict__ out, int heads, int kv_heads, int dim, int vdim) {
+  constexpr bool DELTA = MODE == 1, GATE = MODE == 2, CHANNEL = MODE != 0;      // CHANNEL: a decay a key channel and token
   cima_pdl_wait();
   constexpr int RP = DIMP / REC_SPLIT;                  // rows of a column that one lane keeps
   constexpr int CH = DIMP > 128 ? 8 : 16;               // tokens staged at a time
   constexpr int COLS = REC_COLS * CPT;                  // columns of the block
   __shared__ __align__(16) float sk[CH][DIMP];
   __shared__ __align__(16) float sq[CH][DIMP];
-  __shared__ __align__(16) float sg[DELTA ? CH : 1][DIMP];
+  __shared__ __align__(16) float sg[CHANNEL ? CH : 1][DIMP];
   __shared__ float sv[CH][COLS];
   __shared__ float so[CH][COLS];
   __shared__ float sb[CH];
@@ -62,14 +67,14 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
       const int row = (j >> 2) * 32 + rg * 4 + (j & 3);
       S[x][j] = (col0 + lc + 32 * x < vdim && row < dim) ? st[(size_t)row * vdim + 32 * x] : 0.f;
     }
-  const float dh = DELTA ? 1.f : decay[h];
+  const float dh = CHANNEL ? 1.f : decay[h];
   const int ldo = heads * vdim;
 
   // The next tokens' k, q, g, v and beta travel from global memory into registers while the current ones are worked on
   // from shared memory: every load of a stage is issued before any of them is waited for.
   constexpr int NLD = CH * DIMP / REC_THREADS;          // values of k (and of q, of g) a thread stages
   constexpr int NLV = (CH * COLS + REC_THREADS - 1) / REC_THREADS;
-  float rk[NLD], rq[NLD], rgt[DELTA ? NLD : 1], rv[NLV], rb = 0.f;
+  float rk[NLD], rq[NLD], rgt[CHANNEL ? NLD : 1], rv[NLV], rb = 0.f;
   auto fetch = [&](int t0) {
     const int nt = min(CH, n - t0);
 #pragma unroll
@@ -81,6 +86,12 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
       rk[r] = ok ? cima_to_f32<TQ>(k[row * ldk + (size_t)kvh * dim + i]) : 0.f;
       rq[r] = ok ? cima_to_f32<TQ>(q[row * ldq + (size_t)kvh * dim + i]) : 0.f;
       if (DELTA) rgt[r] = ok ? g[(row * heads + h) * dim + i] : 1.f;
+      if (GATE) {          // k holds the gate's projection z; g its bias, decay its lower bound: f, and 1 - f as the key
+        const float low = ok ? decay[h * dim + i] : 1.f;
+        const float f = ok ? low + (1.0f - low) / (1.0f + expf(-(rk[r] + g[h * dim + i]))) : 1.f;
+        rgt[r] = f;
+        rk[r] = 1.0f - f;
+      }
     }
 #pragma unroll
     for (int r = 0; r < NLV; r++) {
@@ -99,14 +110,14 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
     for (int r = 0; r < NLD; r++) {
       const int idx = threadIdx.x + r * REC_THREADS;
       const int tt = idx / DIMP, i = idx - tt * DIMP;
-      sk[tt][i] = DELTA ? rk[r] : rec_silu(rk[r]);
+      sk[tt][i] = CHANNEL ? rk[r] : rec_silu(rk[r]);
       sq[tt][i] = DELTA ? rq[r] : rec_silu(rq[r]);
-      if (DELTA) sg[tt][i] = rgt[r];
+      if (CHANNEL) sg[tt][i] = rgt[r];
     }
 #pragma unroll
     for (int r = 0; r < NLV; r++) {
       const int idx = threadIdx.x + r * REC_THREADS;
-      if (idx < CH * COLS) sv[idx / COLS][idx % COLS] = DELTA ? rv[r] : rec_silu(rv[r]);
+      if (idx < CH * COLS) sv[idx / COLS][idx % COLS] = CHANNEL ? rv[r] : rec_silu(rv[r]);
     }
     if (DELTA && threadIdx.x < CH) sb[threadIdx.x] = rb;
     __syncthreads();
@@ -135,6 +146,13 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
         const float b = sb[tt];
 #pragma unroll
         for (int x = 0; x < CPT; x++) u[x] = b * (u[x] - rec_sum_over_lanes(p0[x] + p1[x]));
+      } else if (GATE) {
+#pragma unroll
+        for (int j = 0; j < RP; j += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(&sg[tt][(j >> 2) * 32 + rg * 4]);
+#pragma unroll
+          for (int x = 0; x < CPT; x++) { S[x][j] *= g4.x; S[x][j + 1] *= g4.y; S[x][j + 2] *= g4.z; S[x][j + 3] *= g4.w; }
+        }
       } else {
 #pragma unroll
         for (int x = 0; x < CPT; x++)
@@ -179,13 +197,13 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
     }
 }
 
-template <typename TQ, typename TV, bool DELTA>
+template <typename TQ, typename TV, int MODE>
 int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* g, const float* beta,
                       const float* decay, float* state, const int* seq_slot, const int* seq_first_row, float* out,
                       int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   const int cpt = 1;      // two columns a thread (CPT 2) measured slower: half as many blocks, and the chain of a token is no shorter
   const dim3 grid((vdim + REC_COLS * cpt - 1) / (REC_COLS * cpt), heads, n_seqs);
-#define RUN_C(D, C) return cima_launch(k_recurrence<TQ, TV, D, DELTA, C>, grid, dim3(REC_THREADS), (size_t)0, stream, 1, (const TQ*)q, ldq, (const TQ*)k, ldk, \
+#define RUN_C(D, C) return cima_launch(k_recurrence<TQ, TV, D, MODE, C>, grid, dim3(REC_THREADS), (size_t)0, stream, 1, (const TQ*)q, ldq, (const TQ*)k, ldk, \
                                        (const TV*)v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, heads, kv_heads, dim, vdim)
 #define RUN(D) { RUN_C(D, 1); }
   if (dim <= 32) RUN(32);
@@ -255,6 +273,8 @@ k_delta_prepare(const TA* __restrict__ qk, int ldqk, const TA* __restrict__ a, i
 
 // delta != 0: q, k float32 [T, kv_heads * dim] (prepared), v (vdtype) [T, ldv], g [T, heads * dim], beta [T, heads].
 // delta == 0: q, k, v of one dtype (vdtype), SiLU applied here; decay [heads].  out [T, heads * vdim] float32.
+// delta == 2 (the gate rule): q and k of v's dtype, k holding the gate's projection; g its bias and decay its lower bound,
+// both [heads * dim] and shared by all tokens.
 extern "C" int cima_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int vdtype,
                                const float* g, const float* beta, const float* decay, float* state, const int* seq_slot,
                                const int* seq_first_row, float* out, int T, int n_seqs, int heads, int kv_heads, int dim,
@@ -264,16 +284,24 @@ extern "C" int cima_recurrence(const void* q, int ldq, const void* k, int ldk, c
     return cima_fail(CIMA_E_SIZE, "recurrence: %d heads on %d key heads in %d sequences are not accepted", heads, kv_heads, n_seqs);
   if (dim <= 0 || dim > 256 || vdim <= 0) return cima_fail(CIMA_E_SIZE, "recurrence: key size %d must lie in 1..256 and value size %d be positive", dim, vdim);
   if (!state || !out || !q || !k || !v) return cima_fail(CIMA_E_ARG, "recurrence: q, k, v, the state and the output are needed");
+  if (delta == 2) {
+    if (!g || !decay) return cima_fail(CIMA_E_ARG, "recurrence: the gate rule needs the gate's bias and lower bound");
+    int rc2;
+    if (vdtype == CIMA_F32) rc2 = launch_recurrence<float, float, 2>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
+    else if (vdtype == CIMA_BF16) rc2 = launch_recurrence<__nv_bfloat16, __nv_bfloat16, 2>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
+    else return cima_fail(CIMA_E_DTYPE, "recurrence: dtype code %d is neither float32 nor bfloat16", vdtype);
+    return rc2 ? rc2 : cima_launch_result();
+  }
   if (delta && (!g || !beta)) return cima_fail(CIMA_E_ARG, "recurrence: the delta rule needs the tokens' decays and step sizes");
   if (!delta && !decay) return cima_fail(CIMA_E_ARG, "recurrence: the decay rule needs the heads' decays");
   int rc;
   if (delta) {
-    if (vdtype == CIMA_F32) rc = launch_recurrence<float, float, true>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
-    else if (vdtype == CIMA_BF16) rc = launch_recurrence<float, __nv_bfloat16, true>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
+    if (vdtype == CIMA_F32) rc = launch_recurrence<float, float, 1>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
+    else if (vdtype == CIMA_BF16) rc = launch_recurrence<float, __nv_bfloat16, 1>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
     else return cima_fail(CIMA_E_DTYPE, "recurrence: dtype code %d is neither float32 nor bfloat16", vdtype);
   } else {
-    if (vdtype == CIMA_F32) rc = launch_recurrence<float, float, false>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
-    else if (vdtype == CIMA_BF16) rc = launch_recurrence<__nv_bfloat16, __nv_bfloat16, false>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
+    if (vdtype == CIMA_F32) rc = launch_recurrence<float, float, 0>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
+    else if (vdtype == CIMA_BF16) rc = launch_recurrence<__nv_bfloat16, __nv_bfloat16, 0>(q, ldq, k, ldk, v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, n_seqs, heads, kv_heads, dim, vdim, stream);
     else return cima_fail(CIMA_E_DTYPE, "recurrence: dtype code %d is neither float32 nor bfloat16", vdtype);
   }
   return rc ? rc : cima_launch_result();

@@ -124,18 +124,92 @@ k_rope_append_bf16x8(__nv_bfloat16* __restrict__ qkv, int ld, const float* __res
   }
 }
 
+
+// The general form: a warp a head of a row.  Before the rotation the first `norm_dim` values of every q and k head are
+// divided by their root mean square (eps inside the root) and multiplied by a weight of `norm_dim` values, one for all
+// q heads and one for all k heads (no norm where the weights are null); and a row holds `nv` value heads behind its key
+// heads (nv <= nkv: neighbouring key heads share a value head), which go to the first nv heads of the pages' value
+// plane.  Sums of squares, the norm, the angle and the rotation are float32; one rounding at the store.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
+                   const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
+                   const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int nv, int hd,
+                   const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_dim, float eps) {
+  cima_pdl_wait();
+  __shared__ float vals[4][256];
+  const int row = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.x * 4 + warp;
+  if (head >= nh + nkv + nv) return;
+  const int pos = row_pos[row];
+  TA* cache = cache_in;
+  if (cache && pg.ring && pos + pg.ring * pg.page_size < seq_len[row_seq[row]]) cache = nullptr;
+  const int slot = cache ? seq_slot[row_seq[row]] : 0;
+  TA* u = qkv + (size_t)row * ld + (size_t)head * hd;
+  if (head >= nh + nkv) {                              // a value head: to the pages as it is
+    if (!cache) return;
+    TA* dst = cache + pg.offset(slot, pos, 1, head - nh - nkv);
+    for (int d = lane; d < hd; d += 32) dst[d] = u[d];
+    return;
+  }
+  const float* w = head < nh ? q_norm : k_norm;
+  float* x = vals[warp];
+  float ss = 0.f;
+  for (int d = lane; d < hd; d += 32) {
+    const float v = cima_to_f32<TA>(u[d]);
+    x[d] = v;
+    if (d < norm_dim) ss = fmaf(v, v, ss);
+  }
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (w) {
+    const float r = 1.0f / sqrtf(ss / (float)norm_dim + eps);
+    for (int d = lane; d < norm_dim; d += 32) x[d] = x[d] * r * w[d];
+  }
+  __syncwarp();
+  const int half = rotary_dim >> 1;
+  TA* dst = (cache && head >= nh) ? cache + pg.offset(slot, pos, 0, head - nh) : nullptr;
+  for (int d = lane; d < hd; d += 32) {
+    float y = x[d];
+    if (d < rotary_dim) {
+      const int i = d < half ? d : d - half;
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      y = d < half ? x[d] * cs - x[d + half] * sn : x[d - half] * sn + x[d] * cs;
+    }
+    const TA r = cima_from_f32<TA>(y);
+    u[d] = r;
+    if (dst) dst[d] = r;
+  }
+}
+
 // cache may be null (a layer that reads another layer's keys and values writes none).
+// nv: value heads of a row (nkv unless key heads share value heads); q_norm / k_norm (both or neither): the weights of
+// a norm over the first norm_dim values of every q / k head before the rotation.
 // seq_len[i] is the length of sequence i after this step.
 extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_freq, int rotary_dim,
                                 const int* row_pos, const int* row_seq, const int* seq_slot, const int* seq_len,
                                 void* cache, const int* table, int table_width, int ring, int page_size,
-                                int T, int nh, int nkv, int hd, cudaStream_t stream) {
+                                int T, int nh, int nkv, int hd, int nv, const float* q_norm, const float* k_norm, int norm_dim,
+                                float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd > 256 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1))
     return cima_fail(CIMA_E_SIZE, "rope_append: head_dim %d (at most 256) and an even rotary_dim %d <= head_dim are needed", hd, rotary_dim);
-  if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "rope_append: row stride %d is smaller than (heads + 2 kv heads) * head_dim = %d", ld, (nh + 2 * nkv) * hd);
+  if (nv < 0 || nv > nkv || (nv > 0 && nkv % nv)) return cima_fail(CIMA_E_SIZE, "rope_append: %d value heads must divide the %d key heads", nv, nkv);
+  if (ld < (nh + nkv + nv) * hd) return cima_fail(CIMA_E_SIZE, "rope_append: row stride %d is smaller than (heads + key heads + value heads) * head_dim = %d", ld, (nh + nkv + nv) * hd);
+  if ((q_norm != nullptr) != (k_norm != nullptr) || (q_norm && (norm_dim <= 0 || norm_dim > hd)))
+    return cima_fail(CIMA_E_ARG, "rope_append: the norm takes weights for q and for k and 1 <= norm_dim %d <= head_dim %d", norm_dim, hd);
   if (cache && (page_size <= 0 || table_width <= 0)) return cima_fail(CIMA_E_SIZE, "rope_append: page size %d and table width %d must be positive", page_size, table_width);
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+  if (q_norm || nv != nkv) {
+    const dim3 grid((unsigned)((nh + nkv + nv + 3) / 4), (unsigned)T);
+    if (T > 65535) return cima_fail(CIMA_E_SIZE, "rope_append: %d rows exceed one launch of the general kernel; the caller cuts them", T);
+    int rc_;
+    if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+    else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+    else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
+    return rc_ ? rc_ : cima_launch_result();
+  }
   if (dtype == CIMA_F32)
     { int rc_ = cima_launch(k_rope_append<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, hd); if (rc_) return rc_; }
   else if (dtype == CIMA_BF16 && rotary_dim % 16 == 0 && hd % 8 == 0 && ld % 8 == 0 && rotary_dim <= 256 &&

@@ -339,7 +339,13 @@ class Model:
         return self.project(x, batch, info)
 
     def project(self, x: torch.Tensor, batch: StepBatch, info=None) -> torch.Tensor:
-        """Final norm and head at the wanted rows only."""
+        """Final norm and head at the wanted rows only; the logits capped softly where the spec says so."""
+        logits = self._project(x, batch, info)
+        if self.spec.logit_softcap > 0 and logits.shape[0] > 0:
+            self.rt.kernels.softcap(logits, self.spec.logit_softcap)
+        return logits
+
+    def _project(self, x: torch.Tensor, batch: StepBatch, info=None) -> torch.Tensor:
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
         if not batch.want_all_in_order:

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 28
+ABI_VERSION = 29
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -35,7 +35,10 @@ def short_context(head_dim: int) -> int:
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
 # activations of a gated feed-forward's gate (CIMA_ACT_* of csrc/common.cuh), by the names config files use
-ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu_new": 1, "gelu": 2, "relu": 3}
+ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu_new": 1, "gelu": 2, "relu": 3,
+               # min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1): the kernels that take it take the limit L beside the code
+               "swish_clamped": 4}
+GATED_ONLY = 4              # codes from here on are forms of the whole gated middle, not activations of the gate alone
 
 
 class KernelError(RuntimeError):
@@ -55,22 +58,22 @@ _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_
 _SIGNATURES = {
     "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp],
     "cima_rmsnorm": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
-    "cima_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "cima_swiglu": [_vp, _vp, _i, _i, _i, _i, _f, _vp],
     "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
     "cima_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
     "cima_add_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cima_decode_advance": [_vp, _vp, _vp, _vp, _i, _vp],
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _f, _vp],
     "cima_linear_skinny_norm": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_qkv_rope_skinny": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                              _i, _i, _i, _i, _vp],
-    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                             _f, _i, _i, _i, _f, _vp],
-    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _f, _vp],
-    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
-    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _f, _vp],
+                             _f, _i, _i, _i, _f, _i, _i, _vp],
+    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
+    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp],
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                  _f, _i, _vp, _i, _f, _vp],
     "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -96,7 +99,11 @@ _SIGNATURES = {
     "cima_head_linear_append": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp,
                                 _i, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _vp],
-    "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "cima_diff_combine": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
+    "cima_scale_add_group_rmsnorm": [_vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _f, _vp],
+    "cima_cast_rows": [_vp, _vp, _i, _sz, _vp],
+    "cima_softcap": [_vp, _sz, _f, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "cima_sample_general": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -203,14 +210,15 @@ class Kernels:
         self._check(self.lib.cima_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
                                           T, H, eps, self._stream()), "rmsnorm")
 
-    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor, act: int = 0) -> None:
-        """out = act(gate) * up of ``gate_up`` = [gate | up]; ``act`` one of ``ACTIVATIONS``' codes."""
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor, act: int = 0, limit: float = 0.0) -> None:
+        """out = act(gate) * up of ``gate_up`` = [gate | up]; ``act`` one of ``ACTIVATIONS``' codes (``limit`` goes with
+        "swish_clamped")."""
         self._need(gate_up, "gate_up", None, 2); self._need(out, "out", gate_up.dtype, 2)
         T, I2 = gate_up.shape
         if I2 % 2 or tuple(out.shape) != (T, I2 // 2):
             raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} and out {tuple(out.shape)} do not agree")
         if not self._admit("swiglu", T * (I2 + I2 // 2) * out.element_size()): return
-        self._check(self.lib.cima_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), T, I2 // 2, act,
+        self._check(self.lib.cima_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), T, I2 // 2, act, limit,
                                          self._stream()), "swiglu")
 
     def add_residual(self, x: torch.Tensor, delta: torch.Tensor) -> None:
@@ -277,7 +285,7 @@ class Kernels:
 
     def linear_skinny(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                       mode: int, ssq_out: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
-                      xw_out: Optional[torch.Tensor] = None, act: int = 0) -> None:
+                      xw_out: Optional[torch.Tensor] = None, act: int = 0, limit: float = 0.0) -> None:
         """Few rows (<= 8), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K].
         With SK_ACCUM, ``ssq_out`` [M, ceil(N / 16)] receives partial sums of squares of the updated rows and
         ``xw_out`` [M, N] bf16 the updated rows times ``w_next`` (the weight of the norm that follows)."""
@@ -304,7 +312,7 @@ class Kernels:
         if not self._admit(f"linear_skinny[{mode}]", w.numel() * 2 + M * K * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
                                                 M, N, K, K, N, _ptr(ssq_out), _ptr(w_next) if xw_out is not None else None,
-                                                _ptr(xw_out), act, self._stream()), "linear_skinny")
+                                                _ptr(xw_out), act, limit, self._stream()), "linear_skinny")
 
     def linear_skinny_norm(self, xw: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
                            bias: Optional[torch.Tensor], out: torch.Tensor, mode: int, act: int = 0) -> None:
@@ -361,7 +369,7 @@ class Kernels:
                                                   n_kv_heads, head_dim, self._stream()), "qkv_rope_skinny")
 
     def gemm_tc_pair(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                     mode: int, act: int = 0) -> None:
+                     mode: int, act: int = 0, limit: float = 0.0) -> None:
         """out = epilogue(a @ w.T) on the tcgen05 tensor cores, for many rows: bf16 operands by TMA, float32
         accumulation in tensor memory, pairs of SMs on tiles of 256 x 256 (cta_group::2; each SM of a pair stages
         only half of the weight tile).  ``mode`` as for ``linear_skinny`` (SK_*); for SK_SWIGLU ``w`` is [2N, K]."""
@@ -378,7 +386,7 @@ class Kernels:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
         if not self._admit(f"gemm_tcgen05_pair[{mode}]", (w.numel() + M * K) * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_gemm_tcgen05_pair(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M,
-                                                    w.shape[0], K, N, N if mode == SK_SWIGLU else 0, act,
+                                                    w.shape[0], K, N, N if mode == SK_SWIGLU else 0, act, limit,
                                                     self._error_flag.data_ptr(), self._stream()), "gemm_tcgen05_pair")
 
     def error_flag(self, device) -> torch.Tensor:
@@ -399,8 +407,12 @@ class Kernels:
 
     # ------------------------------------------------------------------ attention
     def rope_append(self, qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, row_pos, row_seq, seq_slot,
-                    seq_len, kv, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
-        """Rotate q and k of ``qkv`` in place and append k, v to the layer's pages (``kv`` a LayerKV or None)."""
+                    seq_len, kv, n_heads: int, n_kv_heads: int, head_dim: int, v_heads: Optional[int] = None,
+                    qk_norm=None) -> None:
+        """Rotate q and k of ``qkv`` in place and append k, v to the layer's pages (``kv`` a LayerKV or None).
+        ``v_heads``: value heads of a row where they are fewer than the key heads (neighbouring key heads share one; the
+        pages' value plane holds them in its first heads).  ``qk_norm = (wq, wk, dim, eps)``: before the rotation the first
+        ``dim`` values of every q (k) head are divided by their root mean square and multiplied by wq (wk) [dim]."""
         self._need(qkv, "qkv", None, 2); self._need(inv_freq, "inv_freq", torch.float32, 1)
         for n, t in (("row_pos", row_pos), ("row_seq", row_seq), ("seq_slot", seq_slot), ("seq_len", seq_len)):
             self._need(t, n, torch.int32, 1)
@@ -417,14 +429,26 @@ class Kernels:
             args = (kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size)
         else:
             args = (None, None, 0, 0, 0)
+        nv = n_kv_heads if v_heads is None else int(v_heads)
+        norm = (None, None, 0, 0.0)
+        if qk_norm is not None:
+            wq, wk, nd, eps = qk_norm
+            self._need(wq, "wq", torch.float32, 1); self._need(wk, "wk", torch.float32, 1)
+            if wq.numel() != nd or wk.numel() != nd:
+                raise KernelError(f"rope_append: the norm's weights have {wq.numel()} and {wk.numel()} values, expected {nd}")
+            norm = (wq.data_ptr(), wk.data_ptr(), int(nd), float(eps))
         if not self._admit("rope_append", 2 * qkv.numel() * qkv.element_size()): return
-        self._check(self.lib.cima_rope_append(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], inv_freq.data_ptr(),
-                                              rotary_dim, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
-                                              seq_len.data_ptr(), *args, T, n_heads, n_kv_heads, head_dim, self._stream()), "rope_append")
+        step = 65535 if (qk_norm is not None or nv != n_kv_heads) else T       # the general kernel takes a row a block of grid.y
+        for r0 in range(0, T, step):
+            r1 = min(T, r0 + step)
+            self._check(self.lib.cima_rope_append(qkv[r0:r1].data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], inv_freq.data_ptr(),
+                                                  rotary_dim, row_pos[r0:r1].data_ptr(), row_seq[r0:r1].data_ptr(), seq_slot.data_ptr(),
+                                                  seq_len.data_ptr(), *args, r1 - r0, n_heads, n_kv_heads, head_dim, nv, *norm,
+                                                  self._stream()), "rope_append")
 
     def attention_plain(self, qkv: torch.Tensor, kv, row_pos, row_seq, seq_slot, seq_first_row, out: torch.Tensor,
                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int,
-                        from_cache: bool, sink: float = 0.0) -> None:
+                        from_cache: bool, sink: float = 0.0, keep_first: int = 0, v_group: int = 1) -> None:
         self._need(qkv, "qkv", None, 2); self._need(out, "out", qkv.dtype, 2)
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim):
@@ -442,7 +466,7 @@ class Kernels:
                                                   row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                                                   seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                   n_heads, n_kv_heads, head_dim, scale, window,
-                                                  1 if from_cache else 0, planes, sink, self._stream()), "attention_plain")
+                                                  1 if from_cache else 0, planes, sink, keep_first, v_group, self._stream()), "attention_plain")
 
     def _attention_work(self, qkv, n_heads, n_kv_heads, head_dim, planes: int = 2):
         """(bytes, operations) of an attention launch while a step is profiled: the keys and values of the step's
@@ -474,33 +498,42 @@ class Kernels:
 
     def attention(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                   head_dim: int, scale: float, window: int, from_cache: bool, after_append: bool = False,
-                  sink: float = 0.0) -> None:
+                  sink: float = 0.0, keep_first: int = 0, v_group: int = 1) -> None:
         """Attention of a step's rows: over the step's own keys (a prompt from position 0) or over the
         cache.  Chooses the kernel; every choice computes the same function.  ``after_append``: the kernel
         launched just before wrote nothing but ``qkv`` and the newest position of each sequence in the cache.
-        ``sink``: that many entries of score 0 that carry no value join every row's denominator (0: an ordinary softmax)."""
+        ``sink``: that many entries of score 0 that carry no value join every row's denominator (0: an ordinary softmax).
+        ``keep_first``: with a window, the first so many positions of a sequence stay visible below it.  ``v_group``: that
+        many neighbouring key heads share one value head (a step's rows and the pages' value plane hold
+        n_kv_heads / v_group value heads)."""
+        general = keep_first > 0 or v_group > 1        # the tcgen05 kernels take neither
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and batch.n_rows == batch.n_seqs):
             return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
-                                         scale, window, batch.max_len, early=after_append, sink=sink)
-        many = (qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
+                                         scale, window, batch.max_len, early=after_append, sink=sink,
+                                         keep_first=keep_first, v_group=v_group)
+        many = (not general and qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
                 and getattr(batch, "n_q_tiles_tc", 0) > 0 and getattr(batch, "max_rows", 0) >= TC_ATTENTION_MIN_LEN)
         if from_cache and many and kv.page_size == 64 and kv.storage.numel() // head_dim < 2 ** 31:
             return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, kv=kv, sink=sink)
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
-            return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
+            return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink,
+                                         keep_first=keep_first, v_group=v_group)
         if not from_cache and many:
             return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_prefill(qkv, batch.q_tile_seq, batch.q_tile_row0, batch.seq_first_row, out,
-                                          n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
+                                          n_heads, n_kv_heads, head_dim, scale, window, sink=sink,
+                                          keep_first=keep_first, v_group=v_group)
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
-                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink=sink)
+                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink=sink, keep_first=keep_first,
+                             v_group=v_group)
 
     def attention_prefill(self, qkv: torch.Tensor, tile_seq, tile_row0, seq_first_row, out: torch.Tensor,
-                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, sink: float = 0.0) -> None:
+                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, sink: float = 0.0,
+                          keep_first: int = 0, v_group: int = 1) -> None:
         """Flash attention of ragged prompts that start at position 0 (bf16, head_dim <= 128);
         ``tile_seq``/``tile_row0`` list the blocks of 64 query rows."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
@@ -513,10 +546,11 @@ class Kernels:
         self._check(self.lib.cima_attention_prefill(qkv.data_ptr(), qkv.shape[1], tile_seq.data_ptr(), tile_row0.data_ptr(),
                                                     seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                     tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, sink,
-                                                    self._stream()), "attention_prefill")
+                                                    keep_first, v_group, self._stream()), "attention_prefill")
 
     def attention_extend(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                         head_dim: int, scale: float, window: int, sink: float = 0.0) -> None:
+                         head_dim: int, scale: float, window: int, sink: float = 0.0, keep_first: int = 0,
+                         v_group: int = 1) -> None:
         """Flash attention of sequences that bring several rows to a cache that already holds keys (bf16, pages of
         64, head_dim <= 128): the rows of sequence s stand at positions seq_len[s] - rows .. seq_len[s] - 1, and all
         keys, the step's own included, are read from the layer's pages.  ``batch`` brings the blocks of 64 rows."""
@@ -530,7 +564,8 @@ class Kernels:
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_seq.data_ptr(), batch.q_tile_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(), out.data_ptr(), out.shape[1],
-            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, kv.planes, sink, self._stream()), "attention_extend")
+            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, kv.planes, sink, keep_first, v_group,
+            self._stream()), "attention_extend")
 
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                              head_dim: int, scale: float, window: int, kv=None, sink: float = 0.0) -> None:
@@ -563,7 +598,8 @@ class Kernels:
 
     def attention_decode(self, qkv: torch.Tensor, kv, seq_slot, seq_len, out: torch.Tensor, n_heads: int,
                          n_kv_heads: int, head_dim: int, scale: float, window: int, max_len: int = 0,
-                         n_splits: Optional[int] = None, early: bool = False, sink: float = 0.0) -> None:
+                         n_splits: Optional[int] = None, early: bool = False, sink: float = 0.0, keep_first: int = 0,
+                         v_group: int = 1) -> None:
         """One query per sequence over the paged cache (bf16, pages of 64, head_dim <= 128), keys split
         over ``n_splits`` blocks per (sequence, kv head).  ``max_len`` (0 = unknown) only bounds the
         number of splits chosen here.  ``early``: the kernel launched just before this one wrote neither
@@ -589,7 +625,8 @@ class Kernels:
             if n_splits > 8 and base * 8 >= SPLIT_FEW_BLOCKS:
                 n_splits = 8
             if max_len > 0:
-                n_splits = min(n_splits, -(-max_len // 64))
+                seen = max_len if window <= 0 else min(max_len, window + 64 + -(-keep_first // 64) * 64)      # positions whose pages a row reads
+                n_splits = min(n_splits, -(-seen // 64))
                 # a short context is a few pages: one block reads them in less time than the merge of splits takes
                 if max_len <= short_context(head_dim):
                     n_splits = 1
@@ -602,7 +639,7 @@ class Kernels:
             qkv.data_ptr(), qkv.shape[1], kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, seq_slot.data_ptr(), seq_len.data_ptr(), _ptr(part_o), _ptr(part_ml),
             out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, int(early),
-            kv.planes, sink, self._stream()), "attention_decode")
+            kv.planes, sink, keep_first, v_group, self._stream()), "attention_decode")
         if n_splits > 1:
             self.launches += 1
 
@@ -787,11 +824,16 @@ class Kernels:
     # ------------------------------------------------------------------ recurrent mixers
     def recurrence(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, batch, out: torch.Tensor,
                    heads: int, kv_heads: int, dim: int, vdim: int, g: Optional[torch.Tensor] = None,
-                   beta: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None) -> None:
+                   beta: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None, gate=None) -> None:
         """A linear recurrence over the step's rows, sequence by sequence, with the state S [slots, heads, dim, vdim]
         (float32) carried on.  With ``decay`` [heads]: S <- d S + k v^T, o = S^T q, and q, k, v (one dtype) pass SiLU.
         With ``g`` [T, heads * dim] and ``beta`` [T, heads]: the gated delta rule on prepared float32 q and k
-        ([T, kv_heads * dim]).  q, k, v may be column slices of wider matrices; out [T, heads * vdim] float32."""
+        ([T, kv_heads * dim]).  With ``gate`` = (bias, lower), both float32 [heads * dim]: the gate rule, S <- diag(f) S +
+        (1 - f) v^T with f = lower + (1 - lower) * sigmoid(k + bias) made from the projection that ``k`` holds, o = S^T silu(q),
+        v as it is (q, k, v of one dtype, kv_heads = heads).  q, k, v may be column slices of wider matrices; out
+        [T, heads * vdim] float32."""
+        if gate is not None:
+            return self._recurrence_gate(q, k, v, state, batch, out, heads, kv_heads, dim, vdim, *gate)
         delta = g is not None
         self._need(state, "state", torch.float32, 4); self._need(out, "out", torch.float32, 2)
         T = batch.n_rows
@@ -818,6 +860,25 @@ class Kernels:
                                              dtype_code(v.dtype), _ptr(g), _ptr(beta), _ptr(decay), state.data_ptr(),
                                              batch.seq_slot.data_ptr(), batch.seq_first_row.data_ptr(), out.data_ptr(), T,
                                              batch.n_seqs, heads, kv_heads, dim, vdim, int(delta), self._stream()), "recurrence")
+
+    def _recurrence_gate(self, q, k, v, state, batch, out, heads, kv_heads, dim, vdim, bias, lower) -> None:
+        self._need(state, "state", torch.float32, 4); self._need(out, "out", torch.float32, 2)
+        self._need(bias, "bias", torch.float32, 1); self._need(lower, "lower", torch.float32, 1)
+        T = batch.n_rows
+        for n, t in (("q", q), ("k", k), ("v", v)):
+            if t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != T or not t.is_cuda or t.dtype is not v.dtype:
+                raise KernelError(f"recurrence: {n} {tuple(t.shape)} must be GPU rows of the step, one dtype, unit column stride")
+        if (heads != kv_heads or tuple(state.shape[1:]) != (heads, dim, vdim) or tuple(out.shape) != (T, heads * vdim)
+                or q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim
+                or bias.numel() != heads * dim or lower.numel() != heads * dim):
+            raise KernelError(f"recurrence: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, state {tuple(state.shape)}, "
+                              f"out {tuple(out.shape)} and the gate's vectors do not agree with {heads} heads of {dim} x {vdim}")
+        if not self._admit("recurrence[gate]", batch.n_seqs * heads * dim * vdim * 8 + T * heads * ((2 * dim + vdim) * v.element_size() + vdim * 4),
+                           5.0 * T * heads * dim * vdim): return
+        self._check(self.lib.cima_recurrence(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                                             dtype_code(v.dtype), bias.data_ptr(), None, lower.data_ptr(), state.data_ptr(),
+                                             batch.seq_slot.data_ptr(), batch.seq_first_row.data_ptr(), out.data_ptr(), T,
+                                             batch.n_seqs, heads, kv_heads, dim, vdim, 2, self._stream()), "recurrence")
 
     def delta_prepare(self, qk: torch.Tensor, a: torch.Tensor, b: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
                       qn: torch.Tensor, kn: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, heads: int, kv_heads: int,
@@ -877,6 +938,59 @@ class Kernels:
         yp = (ctypes.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
         wp = (ctypes.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
         self._check(self.lib.cima_rms_mean(yp, wp, len(ys), x.data_ptr(), T, H, eps, int(assign), self._stream()), "rms_mean")
+
+    def diff_combine(self, att: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, heads: int, rep: int,
+                     head_dim: int, v_dim: int, lam: float, post: float, eps: float) -> None:
+        """The end of a differential attention.  ``att`` [T, 2 * heads * head_dim] holds two softmax maps over the same
+        values for every head, in blocks of 2 * rep heads (a key-head pair's map 1 of its rep heads, then map 2 of the
+        same); out[t, h] = rms(a1 - lam * a2) * post * sigmoid(gate[t, h]) over the first ``v_dim`` values of a head,
+        [T, heads * v_dim].  ``gate`` [T, heads] (rows may be slices) or None."""
+        self._need(att, "att", None, 2); self._need(out, "out", att.dtype, 2)
+        T = att.shape[0]
+        if att.shape[1] != 2 * heads * head_dim or tuple(out.shape) != (T, heads * v_dim):
+            raise KernelError(f"diff_combine: att {tuple(att.shape)} and out {tuple(out.shape)} do not agree with {heads} heads of {head_dim} / {v_dim}")
+        if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (T, heads) or gate.dtype is not att.dtype):
+            raise KernelError(f"diff_combine: the gate {tuple(gate.shape)} {gate.dtype} must be [rows, heads] of att's dtype")
+        if not self._admit("diff_combine", (att.numel() + out.numel()) * att.element_size()): return
+        self._check(self.lib.cima_diff_combine(att.data_ptr(), att.shape[1], _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                               out.data_ptr(), dtype_code(att.dtype), T, heads, rep, head_dim, v_dim, lam, post, eps,
+                                               self._stream()), "diff_combine")
+
+    def scale_add_group_rmsnorm(self, x: torch.Tensor, y: Optional[torch.Tensor], alpha: float, w: torch.Tensor, groups: int,
+                                eps: float, h: Optional[torch.Tensor] = None) -> None:
+        """x <- N(alpha * x + y): x, y float32 [T, W] (y None: N(alpha * x)); N divides each of the row's ``groups`` equal
+        consecutive parts by its own root mean square (eps inside the root) and multiplies the whole by w [W].  ``h``
+        (optional, any dtype of the library) receives the new rows too."""
+        self._need(x, "x", torch.float32, 2); self._need(w, "w", torch.float32, 1)
+        T, W = x.shape
+        if groups <= 0 or W % groups or w.numel() != W:
+            raise KernelError(f"scale_add_group_rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)} and {groups} groups do not agree")
+        if y is not None:
+            self._need(y, "y", torch.float32, 2)
+            if y.shape != x.shape:
+                raise KernelError(f"scale_add_group_rmsnorm: y {tuple(y.shape)} is not x's {tuple(x.shape)}")
+        if h is not None:
+            self._need(h, "h", None, 2)
+            if h.shape != x.shape:
+                raise KernelError(f"scale_add_group_rmsnorm: h {tuple(h.shape)} is not x's {tuple(x.shape)}")
+        if not self._admit("scale_add_group_rmsnorm", T * W * (8 + (4 if y is not None else 0) + (h.element_size() if h is not None else 0))): return
+        self._check(self.lib.cima_scale_add_group_rmsnorm(x.data_ptr(), _ptr(y), alpha, w.data_ptr(), _ptr(h),
+                                                          dtype_code(h.dtype) if h is not None else F32, T, groups, W // groups, eps,
+                                                          self._stream()), "scale_add_group_rmsnorm")
+
+    def cast_rows(self, x: torch.Tensor, h: torch.Tensor) -> None:
+        """h = x (float32) in h's dtype."""
+        self._need(x, "x", torch.float32); self._need(h, "h")
+        if h.shape != x.shape:
+            raise KernelError(f"cast_rows: h {tuple(h.shape)} is not x's {tuple(x.shape)}")
+        if not self._admit("cast_rows", x.numel() * (4 + h.element_size())): return
+        self._check(self.lib.cima_cast_rows(x.data_ptr(), h.data_ptr(), dtype_code(h.dtype), x.numel(), self._stream()), "cast_rows")
+
+    def softcap(self, logits: torch.Tensor, cap: float) -> None:
+        """logits <- cap * tanh(logits / cap), in place (float32)."""
+        self._need(logits, "logits", torch.float32)
+        if not self._admit("softcap", logits.numel() * 8): return
+        self._check(self.lib.cima_softcap(logits.data_ptr(), logits.numel(), cap, self._stream()), "softcap")
 
     # ------------------------------------------------------------------ routed feed-forward
     ROUTE_SORT_ROWS = 64        # a step of at most this many rows orders its pairs by expert in the routing launch

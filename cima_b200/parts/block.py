@@ -2,7 +2,9 @@
 (src/models/transformer.rs:1024-1319).  ``parallel``: h = norm(x); x += mixer(conv(h)) + feed_forward(h): one norm
 feeds both sublayers, the mixer optionally through a short causal convolution, the feed-forward optionally absent.
 ``sandwich``: a norm in front of and behind each sublayer, x += m * post(mixer(norm(x))); x += m * post(ffn(norm(x))) with
-the spec's ``residual_mult`` m; the feed-forward with its two norms may be absent.  The block builds its parts from the spec through the
+the spec's ``residual_mult`` m; the feed-forward with its two norms may be absent.  ``postnorm``: the norm stands behind
+the sum, x = norm(a x + mixer(x)); x = norm(a x + feed_forward(x)) with the spec's ``stream_mult`` a; the sublayers read the
+stream itself and the feed-forward may be absent.  The block builds its parts from the spec through the
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
@@ -283,6 +285,93 @@ class SandwichBlock:
         return RowsInfo(norm=next_norm, h=h) if h is not None else None
 
 
+class PostNormBlock:
+    """x = norm1(a x + mixer(x)), then x = norm2(a x + feed_forward(x)) with ``stream_mult`` a: no norm in front of a
+    sublayer, which reads the stream itself (in the activations' dtype), and one behind the sum.  A layer without
+    feed-forward has the first line only.  The sublayers hand their output over as float32 rows (``produce``); the
+    scaled stream, the sum, the norm and the rows the next sublayer reads are one kernel (the norm's ``close``).  The
+    norm is any registered one that offers ``close(x, y, mult)``."""
+
+    def __init__(self, spec, layer: int, rt):
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.mult = float(spec.stream_mult)
+        self.mixer = build_mixer(spec.mixer, layer, rt)
+        self.mixer_post = build_norm(spec.mixer_norm, rt)
+        self.feed_forward = self.ffn_post = None
+        if spec.feed_forward is not None:
+            if spec.ffn_norm is None:
+                raise ValueError(f"layer {layer}: a postnorm block with a feed-forward needs the norm behind it")
+            self.feed_forward = build_feed_forward(spec.feed_forward, layer, rt)
+            self.ffn_post = build_norm(spec.ffn_norm, rt)
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and not hasattr(part, "produce"):
+                raise ValueError(f"layer {layer}: {type(part).__name__} offers no produce(); a postnorm block needs a sublayer's "
+                                 f"output as rows of its own")
+        for norm in (self.mixer_post, self.ffn_post):
+            if norm is not None and not hasattr(norm, "close"):
+                raise ValueError(f"layer {layer}: {type(norm).__name__} offers no close(); a postnorm block needs the sum and "
+                                 f"the norm as one step")
+
+    def _named(self):
+        s = self.spec
+        sfx = s.names.get("suffix", ".weight")
+        out = [(self.mixer, (s.prefix, s.names)), (self.mixer_post, (f"{s.prefix}{s.names['mixer_norm']}{sfx}",))]
+        if self.feed_forward is not None:
+            out += [(self.feed_forward, (s.prefix, s.names)), (self.ffn_post, (f"{s.prefix}{s.names['ffn_norm']}{sfx}",))]
+        return out
+
+    def plan(self) -> Dict[str, TensorSpec]:
+        p: Dict[str, TensorSpec] = {}
+        for part, args in self._named():
+            p.update(part.plan(*args))
+        return p
+
+    def load(self, tensors) -> None:
+        for part, args in self._named():
+            part.load(tensors, *args)
+
+    def state(self) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        for part, args in self._named():
+            if not hasattr(part, "state"):
+                raise NotImplementedError(f"{type(part).__name__} of layer {self.layer} offers no state(): its tensors "
+                                          f"cannot be given back by name")
+            out.update(part.state(*args))
+        return out
+
+    def cache_requests(self, site: int) -> List[object]:
+        return list(self.mixer.cache_requests(site))
+
+    def scratch_row(self) -> int:
+        parts = [p for p in (self.mixer, self.feed_forward) if p is not None]
+        return max(int(getattr(p, "scratch_row", lambda: 0)()) for p in parts) + 2 * self.spec.mixer.hidden
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p, _ in self._named())
+
+    def nbytes(self) -> int:
+        return sum(p.nbytes() for p, _ in self._named())
+
+    def forward(self, x: torch.Tensor, batch, cache, site: int, info=None, next_norm=None):
+        from .norm import RowsInfo
+        if info is not None and getattr(info, "norm", None) is STREAM_ROWS and info.h is not None:
+            h = info.h                                             # the stream in the activations' dtype came along
+        elif self.rt.full_precision:
+            h = x
+        else:
+            h = self.rt.empty(*x.shape)
+            self.rt.kernels.cast_rows(x, h)
+        h = self.mixer_post.close(x, self.mixer.produce(h, batch, cache, site), self.mult)
+        if self.feed_forward is not None:
+            h = self.ffn_post.close(x, self.feed_forward.produce(h, batch), self.mult)
+        return RowsInfo(norm=STREAM_ROWS, h=h)
+
+
+STREAM_ROWS = object()      # a RowsInfo whose ``norm`` is this holds the stream itself in the activations' dtype
+
+
 register_block("prenorm", PreNormBlock)
+register_block("postnorm", PostNormBlock)
 register_block("sandwich", SandwichBlock)
 register_block("parallel", ParallelBlock)

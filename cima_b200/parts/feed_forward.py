@@ -1,7 +1,8 @@
 """Gated feed-forward: x += (act(h Wg^T) * (h Wu^T)) Wd^T in float32, act by the spec's ``activation``: SiLU
 g / (1 + exp(-g)) as the reference has it (src/kernels.cu:81-84; src/models/transformer.rs:1219-1229 and
 :1273-1291), or one of the other entries of ``kernels.ACTIVATIONS`` (tanh or erf GELU, ReLU), which every kernel
-that applies the activation takes as a parameter.  Rows are independent, so a long step is cut into row chunks
+that applies the activation takes as a parameter.  ``swish_clamped`` is a form of the whole middle,
+min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1), with the limit L = ``params["limit"]``.  Rows are independent, so a long step is cut into row chunks
 that bound the [rows, 2I] scratch."""
 from __future__ import annotations
 
@@ -40,7 +41,8 @@ class GatedMLP:
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
         gate, up, down = self._names(prefix, names)
-        self.gate_up = GatedLinearPair(tensors[gate], tensors[up], self.rt, self.spec.activation)
+        self.gate_up = GatedLinearPair(tensors[gate], tensors[up], self.rt, self.spec.activation,
+                                       limit=float(self.spec.params.get("limit", 0.0)))
         self.down = Linear(tensors[down], None, self.rt)
 
     def nbytes(self) -> int:
@@ -71,6 +73,10 @@ class GatedMLP:
             r1 = min(rows, r0 + chunk)
             self.down.accumulate(self.gate_up.activated(h[r0:r1]), x[r0:r1])
         return None
+
+    def produce(self, h, batch) -> torch.Tensor:
+        """The feed-forward's output as float32 rows of its own (what ``forward`` adds into x)."""
+        return self.down.logits(self.gate_up.activated(h))
 
 
 register_feed_forward("gated_mlp", GatedMLP)

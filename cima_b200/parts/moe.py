@@ -28,8 +28,9 @@ class RoutedExperts:
         p = spec.params
         self.E, self.top = int(p["experts"]), int(p["top"])
         self.groups, self.keep, self.scale = int(p.get("groups", 1)), int(p.get("keep", p.get("groups", 1))), float(p.get("scale", 1.0))
-        if spec.activation not in ACTIVATIONS:
-            raise ValueError(f"moe: activation '{spec.activation}' is not one of {sorted(ACTIVATIONS)}")
+        from ..kernels import GATED_ONLY
+        if spec.activation not in ACTIVATIONS or ACTIVATIONS[spec.activation] >= GATED_ONLY:
+            raise ValueError(f"moe: activation '{spec.activation}' is not one of {sorted(a for a, c in ACTIVATIONS.items() if c < GATED_ONLY)}")
         if self.E <= 0 or self.groups <= 0 or self.E % self.groups or not (0 < self.keep <= self.groups):
             raise ValueError(f"moe: {self.E} experts in {self.groups} groups of which {self.keep} stay are not a valid routing")
         if not (0 < self.top <= self.keep * (self.E // self.groups)):

@@ -105,5 +105,44 @@ class DynamicTanh:
         return out
 
 
+class GroupRMSNorm:
+    """RMS norm in groups: a row is split into ``params["groups"]`` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps), and the whole multiplied by a weight of the row's size.  Float32, one rounding at the store."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.groups = int(spec.params.get("groups", 1))
+        if self.groups <= 0 or spec.size % self.groups:
+            raise ValueError(f"group_rmsnorm: {self.groups} groups do not divide the size {spec.size}")
+        self.weight = None
+
+    def plan(self, name: str) -> Dict[str, TensorSpec]:
+        return {name: TensorSpec((self.spec.size,), init="ones_normal")}
+
+    def load(self, tensors, name: str) -> None:
+        self.weight = self.rt.vector(tensors[name])
+
+    def nbytes(self) -> int:
+        return self.weight.numel() * 4
+
+    def state(self, name: str) -> Dict[str, torch.Tensor]:
+        return {name: self.weight}
+
+    graph_safe = True
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        out = self.rt.empty(*x.shape)
+        self.rt.kernels.group_rmsnorm_gate(x, self.weight, None, out, self.groups, self.spec.eps)
+        return out
+
+    def close(self, x: torch.Tensor, y: torch.Tensor, mult: float) -> torch.Tensor:
+        """x <- norm(mult * x + y) in place (the stream, float32); returns the new rows in the activations' dtype (x
+        itself where that is float32)."""
+        h = None if self.rt.full_precision else self.rt.empty(*x.shape)
+        self.rt.kernels.scale_add_group_rmsnorm(x, y, mult, self.weight, self.groups, self.spec.eps, h)
+        return x if h is None else h
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("group_rmsnorm", GroupRMSNorm)
 register_norm("dyt", DynamicTanh)

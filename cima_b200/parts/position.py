@@ -6,6 +6,7 @@ float32 on the device, here the table is made once in float64 and rounded to flo
 sine and cosine are float32 on the device).  With ``params["scaling"]`` = {factor, low, high, original} the
 frequencies are rescaled by their wavelength l = 2 pi / f: kept where l < original / high, divided by ``factor`` where
 l > original / low, and between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+With ``params["linear"]`` = c every frequency is divided by c (positions compressed by c).
 ``none``: nothing rotates.
 A position part offers ``inv_freq`` (float32 [rotary_dim / 2]) and ``rotary_dim``; the attention
 mixer hands both to the kernel that rotates and appends.
@@ -31,6 +32,11 @@ class Rope:
         if scaling:
             inv = rescale_by_wavelength(inv, float(scaling["factor"]), float(scaling["low"]), float(scaling["high"]),
                                         float(scaling["original"]))
+        linear = spec.params.get("linear") if spec.params else None
+        if linear is not None:
+            if float(linear) <= 0:
+                raise ValueError(f"rope: the linear factor {linear} must be positive")
+            inv = inv / float(linear)
         self.inv_freq = inv.to(torch.float32).to(rt.device).contiguous()
 
 

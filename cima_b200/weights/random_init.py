@@ -32,7 +32,7 @@ def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, 
     """The tensor ``name`` drawn from the generator seeded by (seed, name), in slabs of ``_SLAB`` values in float32
     that are rounded into ``dtype`` as they come.  On the CPU a slab (a multiple of 16 values) continues the
     generator's sequence exactly where the last one ended, so the values do not depend on the slab size."""
-    if spec.init not in ("normal", "ones_normal", "mean"):
+    if spec.init not in ("normal", "ones_normal", "mean", "unit"):
         raise ValueError(f"unknown init '{spec.init}' for tensor '{name}'")
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
@@ -42,6 +42,10 @@ def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, 
     scratch = torch.empty(min(n, _SLAB), dtype=torch.float32, device=device)
     for lo in range(0, n, _SLAB):
         part = scratch[:min(_SLAB, n - lo)]
+        if spec.init == "unit":                      # a bound or a rate in (0, 1)
+            part.uniform_(0.0, 1.0, generator=g)
+            flat[lo:lo + part.numel()].copy_(part)
+            continue
         part.normal_(0.0, spec.std, generator=g)
         if spec.init in ("ones_normal", "mean"):
             part += 1.0

@@ -57,10 +57,19 @@ class ReferenceKernels:
             return torch.clamp(g, min=0.0)
         return g / (1.0 + torch.exp(-g))
 
-    def swiglu(self, gate_up, out, act=0):
+    @classmethod
+    def gated(cls, g, u, act, limit=0.0):
+        """The gated middle by its code: act(g) * u, or (4) the clamped form with its limit."""
+        if act == 4:
+            g = torch.clamp(g, max=limit)
+            u = torch.clamp(u, min=-limit, max=limit)
+            return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+        return cls.gate_act(g, act) * u
+
+    def swiglu(self, gate_up, out, act=0, limit=0.0):
         I = gate_up.shape[1] // 2
         g, u = gate_up[:, :I].to(self.compute), gate_up[:, I:].to(self.compute)
-        out.copy_((self.gate_act(g, act) * u).to(out.dtype))
+        out.copy_(self.gated(g, u, act, limit).to(out.dtype))
 
     def add_residual(self, x, delta):
         x.add_(delta.float())
@@ -95,12 +104,12 @@ class ReferenceKernels:
         h = (xw.to(self.compute) * inv).to(torch.bfloat16)
         self.linear_skinny(h, w, bias, out, mode, act=act)
 
-    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None, w_next=None, xw_out=None, act=0):
+    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None, w_next=None, xw_out=None, act=0, limit=0.0):
         y = a.to(self.compute) @ w.to(self.compute).t()
         if mode == SK_SWIGLU:
             I = w.shape[0] // 2
             g, u = y[:, :I], y[:, I:]
-            out.copy_((self.gate_act(g, act) * u).to(out.dtype))
+            out.copy_(self.gated(g, u, act, limit).to(out.dtype))
             return
         if bias is not None:
             y = y + bias.to(self.compute)
@@ -129,11 +138,20 @@ class ReferenceKernels:
         self.rope_append(y, inv_freq, head_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim)
         qkv.copy_(y.to(qkv.dtype))
 
-    def rope_append(self, qkv, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim):
+    def rope_append(self, qkv, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim,
+                    v_heads=None, qk_norm=None):
         T = qkv.shape[0]
         half = rotary_dim // 2
-        heads = qkv[:, :(n_heads + 2 * n_kv_heads) * head_dim].view(T, n_heads + 2 * n_kv_heads, head_dim)
+        nv = n_kv_heads if v_heads is None else v_heads
+        heads = qkv[:, :(n_heads + n_kv_heads + nv) * head_dim].view(T, n_heads + n_kv_heads + nv, head_dim)
         rot = heads[:, :n_heads + n_kv_heads, :].to(self.compute)
+        if qk_norm is not None:
+            wq, wk, nd, eps = qk_norm
+            part = rot[..., :nd]
+            part = part / torch.sqrt((part * part).mean(dim=-1, keepdim=True) + eps)
+            part[:, :n_heads] = part[:, :n_heads] * wq.to(self.compute)
+            part[:, n_heads:] = part[:, n_heads:] * wk.to(self.compute)
+            rot[..., :nd] = part
         if half:
             ang = (row_pos[:T].to(torch.float32)[:, None] * inv_freq[None, :]).to(self.compute)
             c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
@@ -149,27 +167,28 @@ class ReferenceKernels:
                 continue          # a later position of this step takes the place
             page, off = _page_offset(kv, slot, int(row_pos[r]))
             kv.storage[page, 0, :, off, :] = heads[r, n_heads:n_heads + n_kv_heads, :]
-            kv.storage[page, 1, :, off, :] = heads[r, n_heads + n_kv_heads:, :]
+            kv.storage[page, 1, :nv, off, :] = heads[r, n_heads + n_kv_heads:, :]
 
     def attention(self, qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, from_cache, after_append=False,
-                  sink=0.0):
+                  sink=0.0, keep_first=0, v_group=1):
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
-                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink)
+                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink, keep_first, v_group)
 
     def attention_plain(self, qkv, kv, row_pos, row_seq, seq_slot, seq_first_row, out, n_heads, n_kv_heads,
-                        head_dim, scale, window, from_cache, sink=0.0):
+                        head_dim, scale, window, from_cache, sink=0.0, keep_first=0, v_group=1):
         T = qkv.shape[0]
         rep = n_heads // n_kv_heads
         vplane = int(getattr(kv, "planes", 2)) - 1 if from_cache else 1      # one plane: the values are the keys
-        cols = (n_heads + (0 if from_cache else 2 * n_kv_heads)) * head_dim
+        cols = (n_heads + (0 if from_cache else n_kv_heads + n_kv_heads // v_group)) * head_dim
         heads = qkv[:, :cols].view(T, cols // head_dim, head_dim)
         for r in range(T):
             pos, seq = int(row_pos[r]), int(row_seq[r])
             lo = max(0, pos + 1 - window) if window > 0 else 0
+            seen = list(range(0, min(keep_first, lo))) + list(range(lo, pos + 1))      # kept first positions, then the window
             if from_cache:
                 slot = int(seq_slot[seq])
                 ks, vs = [], []
-                for j in range(lo, pos + 1):
+                for j in seen:
                     page, off = _page_offset(kv, slot, j)
                     ks.append(kv.storage[page, 0, :, off, :])
                     vs.append(kv.storage[page, vplane, :, off, :])
@@ -177,8 +196,9 @@ class ReferenceKernels:
                 v = torch.stack(vs).to(self.compute)
             else:
                 first = int(seq_first_row[seq])
-                k = heads[first + lo:first + pos + 1, n_heads:n_heads + n_kv_heads, :].to(self.compute)
-                v = heads[first + lo:first + pos + 1, n_heads + n_kv_heads:, :].to(self.compute)
+                rows = torch.as_tensor(seen, dtype=torch.long) + first
+                k = heads[rows, n_heads:n_heads + n_kv_heads, :].to(self.compute)
+                v = heads[rows, n_heads + n_kv_heads:, :].to(self.compute)
             q = heads[r, :n_heads, :].to(self.compute)
             for h in range(n_heads):
                 g = h // rep
@@ -189,7 +209,7 @@ class ReferenceKernels:
                     w = e / (e.sum() + sink * torch.exp(-m))
                 else:
                     w = torch.softmax(s, dim=0)
-                out[r, h * head_dim:(h + 1) * head_dim] = (w @ v[:, g, :]).to(out.dtype)
+                out[r, h * head_dim:(h + 1) * head_dim] = (w @ v[:, g // v_group, :]).to(out.dtype)
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, tokens):
@@ -312,10 +332,23 @@ def _silu(z):
     return z / (1.0 + torch.exp(-z))
 
 
-def _recurrence(self, q, k, v, state, batch, out, heads, kv_heads, dim, vdim, g=None, beta=None, decay=None):
+def _recurrence(self, q, k, v, state, batch, out, heads, kv_heads, dim, vdim, g=None, beta=None, decay=None, gate=None):
     delta = g is not None
     T = batch.n_rows
     qf, kf, vf = q.float().view(T, kv_heads, dim), k.float().view(T, kv_heads, dim), v.float().view(T, heads, vdim)
+    if gate is not None:
+        bias, lower = (t.view(1, heads, dim) for t in gate)
+        f = lower + (1.0 - lower) * torch.sigmoid(kf + bias)
+        qf = _silu(qf)
+        for s in range(batch.n_seqs):
+            lo, hi = int(batch.seq_first_row[s]), int(batch.seq_first_row[s + 1])
+            slot = int(batch.seq_slot[s])
+            S = state[slot].clone()
+            for t in range(lo, hi):
+                S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * vf[t][:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, qf[t]).reshape(-1)
+            state[slot] = S
+        return
     if not delta:
         qf, kf, vf = _silu(qf), _silu(kf), _silu(vf)
     share = heads // kv_heads
@@ -397,6 +430,39 @@ def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False):
             acc = acc + wgt[t, j] * (down[e].float() @ z)
         x[t] = acc if assign else x[t] + acc
 
+
+# ---------------------------------------------------------------------- differential attention, the norm behind a sum
+def _diff_combine(self, att, gate, out, heads, rep, head_dim, v_dim, lam, post, eps):
+    T = att.shape[0]
+    a = att.float().view(T, heads // rep, 2, rep, head_dim)[..., :v_dim]
+    o = (a[:, :, 0] - lam * a[:, :, 1]).reshape(T, heads, v_dim)
+    o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * post
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())[:, :, None]
+    out.copy_(o.reshape(T, heads * v_dim).to(out.dtype))
+
+
+def _scale_add_group_rmsnorm(self, x, y, alpha, w, groups, eps, h=None):
+    T, W = x.shape
+    z = alpha * x if y is None else alpha * x + y
+    z = z.view(T, groups, W // groups)
+    z = (z / torch.sqrt((z * z).mean(-1, keepdim=True) + eps)).view(T, W) * w
+    x.copy_(z)
+    if h is not None:
+        h.copy_(z.to(h.dtype))
+
+
+def _cast_rows(self, x, h):
+    h.copy_(x.to(h.dtype))
+
+
+def _softcap(self, logits, cap):
+    logits.copy_(cap * torch.tanh(logits / cap))
+
+
+for _name, _fn in (("diff_combine", _diff_combine), ("scale_add_group_rmsnorm", _scale_add_group_rmsnorm), ("cast_rows", _cast_rows),
+                   ("softcap", _softcap)):
+    setattr(ReferenceKernels, _name, _fn)
 
 for _name, _fn in (("dyt", _dyt), ("dyt_add", _dyt_add), ("embed_bigram", _embed_bigram), ("recurrence", _recurrence),
                    ("delta_prepare", _delta_prepare), ("group_rmsnorm_gate", _group_rmsnorm_gate), ("rms_mean", _rms_mean),
