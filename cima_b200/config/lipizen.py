@@ -195,6 +195,14 @@ class LipizenConfig:
         W, eps = self.width, self.norm_eps
         norm = NormSpec(kind="group_rmsnorm", size=W, eps=eps, params={"groups": self.norm_groups})
         blocks = []
+        # what a layer's pages must keep: the widest mask among the layers that read them (itself and those that name it)
+        keeps: Dict[int, int] = {}
+        for i, L in enumerate(self.layers):
+            if L.kind == "attention":
+                a = L.attention
+                src = i if a.kv_from is None else a.kv_from
+                every = a.window == 0 or a.keep_first > 0
+                keeps[src] = 0 if every or keeps.get(src, -1) == 0 else max(keeps.get(src, -1), a.window)
         for i, L in enumerate(self.layers):
             names = {"mixer_norm": "norm1", "ffn_norm": "norm2", "gate": "mlp.gate", "up": "mlp.up", "down": "mlp.down", "suffix": ""}
             if L.kind == "attention":
@@ -203,7 +211,8 @@ class LipizenConfig:
                        if a.rot_dims else PositionSpec(kind="none", head_dim=a.dim, rotary_dim=0, theta=0.0))
                 mixer = MixerSpec(kind="diff_attention", hidden=W, n_heads=a.heads, n_kv_heads=a.kv_heads, head_dim=a.dim,
                                   window=a.window, scale=a.scale, position=pos, cache_from=a.kv_from,
-                                  params={"v_dim": a.vdim, "diff": a.diff, "taps": a.conv, "keep_first": a.keep_first, "eps": eps})
+                                  params={"v_dim": a.vdim, "diff": a.diff, "taps": a.conv, "keep_first": a.keep_first, "eps": eps,
+                                          "cache_window": keeps.get(i, 0)})
                 names.update({k: f"mix.{k}" for k in ("q", "k", "v", "g", "o", "lq1", "lk1", "lq2", "lk2")})
             else:
                 g = L.gate

@@ -167,8 +167,10 @@ class DiffAttention:
     def cache_requests(self, site: int) -> List[object]:
         reqs: List[object] = list(self.conv.cache_requests(site)) if self.conv is not None else []
         if self.writes:
-            # kept first positions live below the window: every page stays (a ring would hand their pages on)
-            reqs.append(KVRequest(2 * self.kv_heads, self.hd, 0 if self.keep_first > 0 else self.spec.window))
+            # kept first positions live below the window: every page stays (a ring would hand their pages on);
+            # ``cache_window`` is the widest mask of the layers that read these pages, where the spec gives it
+            own = 0 if self.keep_first > 0 else self.spec.window
+            reqs.append(KVRequest(2 * self.kv_heads, self.hd, int(self.spec.params.get("cache_window", own))))
         return reqs
 
     # ------------------------------------------------------------------ step

@@ -99,7 +99,8 @@ def plain_rotate(x: torch.Tensor, dims: int, base: float, factor: float, first_p
 
 
 def plain_visible(i: int, j: int, size: int, keep_first: int) -> bool:
-    return j <= i and (i - j < size or j < keep_first)
+    """``size`` 0: no window, every earlier position is seen."""
+    return j <= i and (size <= 0 or i - j < size or j < keep_first)
 
 
 def plain_softmax_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, size: int, keep_first: int):
@@ -119,8 +120,10 @@ def plain_keys_values(h, W, m: dict, eps: float):
     (convolved only)."""
     G, dim, vdim = m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    k = plain_causal_conv(h @ W["k"].T, W["k.conv"]).reshape(T, G * 2, dim)
-    v = plain_causal_conv(h @ W["v"].T, W["v.conv"]).reshape(T, G, vdim)
+    k, v = h @ W["k"].T, h @ W["v"].T
+    if m.get("conv"):
+        k, v = plain_causal_conv(k, W["k.conv"]), plain_causal_conv(v, W["v.conv"])
+    k, v = k.reshape(T, G * 2, dim), v.reshape(T, G, vdim)
     k = plain_rms(k, eps) * W["k.norm"]
     rot = m.get("rot") or {}
     k = plain_rotate(k, rot.get("dims", 0), rot.get("base", 1.0), (rot.get("scaling") or {}).get("factor", 1.0))
@@ -132,14 +135,17 @@ def plain_diff_attention(h, W, m: dict, eps: float, keys_values=None):
     has none of its own."""
     H, G, dim, vdim, d = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["diff"]
     T = h.shape[0]
-    q = plain_causal_conv(h @ W["q"].T, W["q.conv"]).reshape(T, H * 2, dim)
-    q = plain_rms(q, eps) * W["q.norm"]
+    q = h @ W["q"].T
+    if m.get("conv"):
+        q = plain_causal_conv(q, W["q.conv"])
+    q = plain_rms(q.reshape(T, H * 2, dim), eps) * W["q.norm"]
     rot = m.get("rot") or {}
     q = plain_rotate(q, rot.get("dims", 0), rot.get("base", 1.0), (rot.get("scaling") or {}).get("factor", 1.0)).reshape(T, H, 2, dim)
     k, v = keys_values if keys_values is not None else plain_keys_values(h, W, m, eps)
     lam = math.exp(float((W["lq1"] * W["lk1"]).sum())) - math.exp(float((W["lq2"] * W["lk2"]).sum())) + d
     gate = torch.sigmoid(h @ W["g"].T)                         # [T, H]
-    size, keep = m["mask"]["size"], m["mask"].get("keep_first", 0)
+    mask = m.get("mask") or {}
+    size, keep = mask.get("size") or 0, mask.get("keep_first") or 0
     heads = []
     for hh in range(H):
         g = hh // (H // G)
