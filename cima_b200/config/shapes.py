@@ -2,7 +2,9 @@
 Vunovik decoder at the same widths, heads, feed-forward sizes and vocabularies (no trained model of that design
 exists; they serve measurements beside the Qwen2 shape of equal size), and shapes of the Gisirax decoder at those
 widths: two delta-rule layers, then one layer of softmax attention beside a decay recurrence, every layer with routed
-experts of which a token uses as many values of a feed-forward's middle as the Qwen2 shape has.
+experts of which a token uses as many values of a feed-forward's middle as the Qwen2 shape has, and shapes of the
+Lipizen decoder at those widths: of every four layers one runs the gate recurrence and three differential attention (the
+last of them on the keys and values of the one before it), every layer with the dense feed-forward of the Qwen2 shape.
 Every entry is a complete config.json; nothing here is read by the model code."""
 
 
@@ -45,11 +47,37 @@ def _gisirax(layers, width, heads, kv_heads, dim, ff, vocab, experts=16, top=4, 
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 127}}, "layers": out}
 
 
-# the Qwen2 shape that a Vunovik or Gisirax shape is measured beside
-TWINS = {"gisirax-0.5b": "qwen2.5-0.5b", "gisirax-1.5b": "qwen2.5-1.5b", "gisirax-3b": "qwen2.5-3b", "gisirax-7b": "qwen2.5-7b",
+def _lipizen(layers, width, heads, kv_heads, dim, ff, vocab, taps=4, window=1024, keep_first=64, groups=2):
+    """Layers 0 and 2 of every four run differential attention with keys of their own, layer 1 the gate recurrence, layer 3
+    differential attention on layer 2's keys and values.  A head has two maps of ``dim / 2`` and values of ``dim``, so the
+    projections have the Qwen2 shape's sizes."""
+    out = []
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    for i in range(layers):
+        if i % 4 == 1:
+            out.append({"type": "hgrn2", "mixer": {"heads": heads, "dim": dim, "vdim": dim}, "mlp": mlp})
+            continue
+        mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5, "diff": 0.8,
+                 "conv": taps, "rot": {"dims": dim // 2, "base": 1000000.0, "scaling": {"factor": 4.0}},
+                 "mask": {"size": window, "keep_first": keep_first}}
+        if i % 4 == 3:
+            mixer["kv_from"] = i - 1
+        out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Lipizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": groups}, "postln_alpha": 1.0,
+            "logit_softcap": 30.0, "layers": out}
+
+
+# the Qwen2 shape that a Vunovik, Gisirax or Lipizen shape is measured beside
+TWINS = {"lipizen-0.5b": "qwen2.5-0.5b", "lipizen-1.5b": "qwen2.5-1.5b", "lipizen-3b": "qwen2.5-3b", "lipizen-7b": "qwen2.5-7b",
+         "gisirax-0.5b": "qwen2.5-0.5b", "gisirax-1.5b": "qwen2.5-1.5b", "gisirax-3b": "qwen2.5-3b", "gisirax-7b": "qwen2.5-7b",
          "vunovik-0.5b": "qwen2.5-0.5b", "vunovik-1.5b": "qwen2.5-1.5b", "vunovik-3b": "qwen2.5-3b", "vunovik-7b": "qwen2.5-7b"}
 
 SHAPES = {
+    "lipizen-tiny": _lipizen(4, 128, 4, 2, 32, 256, 512, taps=3, window=96, keep_first=4),
+    "lipizen-0.5b": _lipizen(24, 896, 14, 2, 64, 4864, 151936),
+    "lipizen-1.5b": _lipizen(28, 1536, 12, 2, 128, 8960, 151936),
+    "lipizen-3b": _lipizen(36, 2048, 16, 2, 128, 11008, 151936),
+    "lipizen-7b": _lipizen(28, 3584, 28, 4, 128, 18944, 152064),
     "gisirax-tiny": _gisirax(3, 128, 4, 2, 32, 256, 512, experts=8, top=2, groups=2, keep=1, taps=3, rank=16),
     "gisirax-0.5b": _gisirax(24, 896, 14, 2, 64, 4864, 151936),
     "gisirax-1.5b": _gisirax(28, 1536, 12, 2, 128, 8960, 151936),
