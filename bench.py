@@ -123,7 +123,7 @@ def design_bench(a) -> int:
         return raw
 
     def load(raw, batch):
-        per_seq = a.prompt + steps + warmup + 64
+        per_seq = a.prompt + max(steps + warmup, 192 if a.per_kernel else 0) + 64   # the launch profile replays the step 176 times
         return cima_b200.load(config=raw, seed=0, draw="device", dtype="bfloat16", device=dev, max_seqs=batch,
                               max_tokens=max(batch * (-(-per_seq // 64) * 64), 2048 + 64), max_batch=batch,
                               pipeline=False, verbose=False)
