@@ -47,7 +47,7 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
   constexpr int RP = DIMP / REC_SPLIT;                  // rows of a column that one lane keeps
   constexpr int CH = DIMP > 128 ? 8 : 16;               // tokens staged at a time
   constexpr int COLS = REC_COLS * CPT;                  // columns of the block
-  __shared__ __align__(16) float sk[CH][DIMP];
+  __shared__ __align__(16) float sk[GATE ? 1 : CH][DIMP];     // the gate rule writes (1 - f) v: it needs no key
   __shared__ __align__(16) float sq[CH][DIMP];
   __shared__ __align__(16) float sg[CHANNEL ? CH : 1][DIMP];
   __shared__ float sv[CH][COLS];
@@ -74,7 +74,18 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
   // from shared memory: every load of a stage is issued before any of them is waited for.
   constexpr int NLD = CH * DIMP / REC_THREADS;          // values of k (and of q, of g) a thread stages
   constexpr int NLV = (CH * COLS + REC_THREADS - 1) / REC_THREADS;
-  float rk[NLD], rq[NLD], rgt[CHANNEL ? NLD : 1], rv[NLV], rb = 0.f;
+  float rk[NLD], rq[NLD], rgt[DELTA ? NLD : 1], rv[NLV], rb = 0.f;
+  // The gate rule: k holds the gate's projection z, g its bias and decay its lower bound (the same for every token: a
+  // thread stages the same channels in every round and keeps theirs).  A channel beyond the key size gets the bound 1: f = 1.
+  float glow[GATE ? NLD : 1], gbias[GATE ? NLD : 1];
+  if (GATE) {
+#pragma unroll
+    for (int r = 0; r < NLD; r++) {
+      const int i = (threadIdx.x + r * REC_THREADS) % DIMP;
+      glow[r] = i < dim ? decay[h * dim + i] : 1.f;
+      gbias[r] = i < dim ? g[h * dim + i] : 0.f;
+    }
+  }
   auto fetch = [&](int t0) {
     const int nt = min(CH, n - t0);
 #pragma unroll
@@ -86,12 +97,6 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
       rk[r] = ok ? cima_to_f32<TQ>(k[row * ldk + (size_t)kvh * dim + i]) : 0.f;
       rq[r] = ok ? cima_to_f32<TQ>(q[row * ldq + (size_t)kvh * dim + i]) : 0.f;
       if (DELTA) rgt[r] = ok ? g[(row * heads + h) * dim + i] : 1.f;
-      if (GATE) {          // k holds the gate's projection z; g its bias, decay its lower bound: f, and 1 - f as the key
-        const float low = ok ? decay[h * dim + i] : 1.f;
-        const float f = ok ? low + (1.0f - low) / (1.0f + expf(-(rk[r] + g[h * dim + i]))) : 1.f;
-        rgt[r] = f;
-        rk[r] = 1.0f - f;
-      }
     }
 #pragma unroll
     for (int r = 0; r < NLV; r++) {
@@ -110,9 +115,10 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
     for (int r = 0; r < NLD; r++) {
       const int idx = threadIdx.x + r * REC_THREADS;
       const int tt = idx / DIMP, i = idx - tt * DIMP;
-      sk[tt][i] = CHANNEL ? rk[r] : rec_silu(rk[r]);
+      if (!GATE) sk[tt][i] = DELTA ? rk[r] : rec_silu(rk[r]);
       sq[tt][i] = DELTA ? rq[r] : rec_silu(rq[r]);
-      if (CHANNEL) sg[tt][i] = rgt[r];
+      if (DELTA) sg[tt][i] = rgt[r];
+      if (GATE) sg[tt][i] = glow[r] + (1.0f - glow[r]) / (1.0f + expf(-(rk[r] + gbias[r])));
     }
 #pragma unroll
     for (int r = 0; r < NLV; r++) {
@@ -122,6 +128,46 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
     if (DELTA && threadIdx.x < CH) sb[threadIdx.x] = rb;
     __syncthreads();
     if (t0 + CH < n) fetch(t0 + CH);
+    if constexpr (GATE) {
+      // Nothing of a token's read-out feeds the next token's update, so four tokens are taken together: their updates
+      // follow one another row by row (S <- u + f (S - u), which is f S + (1 - f) u), their sums over the lanes run side
+      // by side.  A token's own arithmetic is the same wherever it stands among the four.
+      static_assert(CPT == 1 || !GATE, "the gate rule runs one column a thread");
+      constexpr int TB = 4;
+      for (int tt = 0; tt < nt; tt += TB) {
+        float o0[TB], o1[TB];
+#pragma unroll
+        for (int x = 0; x < TB; x++) {
+          o0[x] = o1[x] = 0.f;
+          if (tt + x < nt) {
+            const float u = sv[tt + x][lc];
+#pragma unroll
+            for (int j = 0; j < RP; j += 4) {
+              const int i = (j >> 2) * 32 + rg * 4;
+              const float4 g4 = *reinterpret_cast<const float4*>(&sg[tt + x][i]);
+              const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt + x][i]);
+              S[0][j] = fmaf(g4.x, S[0][j] - u, u); S[0][j + 1] = fmaf(g4.y, S[0][j + 1] - u, u);
+              S[0][j + 2] = fmaf(g4.z, S[0][j + 2] - u, u); S[0][j + 3] = fmaf(g4.w, S[0][j + 3] - u, u);
+              o0[x] = fmaf(S[0][j], q4.x, o0[x]); o1[x] = fmaf(S[0][j + 1], q4.y, o1[x]);
+              o0[x] = fmaf(S[0][j + 2], q4.z, o0[x]); o1[x] = fmaf(S[0][j + 3], q4.w, o1[x]);
+            }
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < TB; x++) o0[x] += o1[x];
+#pragma unroll
+        for (int x = 0; x < TB; x++) o0[x] += __shfl_xor_sync(0xffffffffu, o0[x], 4);
+#pragma unroll
+        for (int x = 0; x < TB; x++) o0[x] += __shfl_xor_sync(0xffffffffu, o0[x], 8);
+#pragma unroll
+        for (int x = 0; x < TB; x++) o0[x] += __shfl_xor_sync(0xffffffffu, o0[x], 16);
+        if (rg == 0) {
+#pragma unroll
+          for (int x = 0; x < TB; x++)
+            if (tt + x < nt) so[tt + x][lc] = o0[x];
+        }
+      }
+    } else {
 #pragma unroll 2
     for (int tt = 0; tt < nt; tt++) {
       float u[CPT];
@@ -146,13 +192,6 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
         const float b = sb[tt];
 #pragma unroll
         for (int x = 0; x < CPT; x++) u[x] = b * (u[x] - rec_sum_over_lanes(p0[x] + p1[x]));
-      } else if (GATE) {
-#pragma unroll
-        for (int j = 0; j < RP; j += 4) {
-          const float4 g4 = *reinterpret_cast<const float4*>(&sg[tt][(j >> 2) * 32 + rg * 4]);
-#pragma unroll
-          for (int x = 0; x < CPT; x++) { S[x][j] *= g4.x; S[x][j + 1] *= g4.y; S[x][j + 2] *= g4.z; S[x][j + 3] *= g4.w; }
-        }
       } else {
 #pragma unroll
         for (int x = 0; x < CPT; x++)
@@ -180,6 +219,7 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
         const float o = rec_sum_over_lanes(o0[x] + o1[x]);
         if (rg == 0) so[tt][lc + 32 * x] = o;
       }
+    }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nt * COLS; idx += REC_THREADS) {
