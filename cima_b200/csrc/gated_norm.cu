@@ -76,8 +76,21 @@ __global__ void __launch_bounds__(256)
 k_cast_rows(const float* __restrict__ x, TH* __restrict__ h, size_t total) {
   cima_pdl_wait();
   cima_pdl_trigger();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < total) h[i] = cima_from_f32<TH>(x[i]);
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;      // four values a thread
+  if (i + 4 <= total && (((uintptr_t)x | (uintptr_t)h) & 15) == 0) {
+    const float4 v = *reinterpret_cast<const float4*>(x + i);
+    if constexpr (sizeof(TH) == 2) {
+      uint2 t;
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&t);
+      h2[0] = __floats2bfloat162_rn(v.x, v.y);
+      h2[1] = __floats2bfloat162_rn(v.z, v.w);
+      *reinterpret_cast<uint2*>(h + i) = t;
+    } else {
+      *reinterpret_cast<float4*>(h + i) = v;
+    }
+    return;
+  }
+  for (size_t j = i; j < total && j < i + 4; j++) h[j] = cima_from_f32<TH>(x[j]);
 }
 
 template <typename TG, typename TO>
@@ -213,7 +226,7 @@ extern "C" int cima_scale_add_group_rmsnorm(float* x, const float* y, float alph
 // h = x in another dtype (the rows a sublayer reads where no norm stands in front of it).
 extern "C" int cima_cast_rows(const float* x, void* h, int hdtype, size_t total, cudaStream_t stream) {
   if (total == 0) return 0;
-  const size_t blocks = (total + 255) / 256;
+  const size_t blocks = (total + 1023) / 1024;
   if (blocks > 0x7fffffffull) return cima_fail(CIMA_E_SIZE, "cast_rows: %zu values exceed one launch", total);
   int rc;
   if (hdtype == CIMA_BF16) rc = cima_launch(k_cast_rows<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, 1, x, (__nv_bfloat16*)h, total);

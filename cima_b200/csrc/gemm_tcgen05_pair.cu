@@ -197,8 +197,21 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         if (GATED) {
           float u[32];
           tmem_ld32(acc + (unsigned)(BN / 2 + c0), u);
+          // one loop per form: the four epilogue warps have nothing to hide a branch or a call behind
+          if (a.act == CIMA_ACT_SILU) {
 #pragma unroll
-          for (int e = 0; e < 32; e++) v[e] = a.act == CIMA_ACT_SILU ? v[e] / (1.0f + expf(-v[e])) * u[e] : cima_gated(v[e], u[e], a.act, a.act_limit);
+            for (int e = 0; e < 32; e++) v[e] = v[e] / (1.0f + expf(-v[e])) * u[e];
+          } else if (a.act == CIMA_GATED_SWISH_CLAMPED) {
+            const float lim = a.act_limit;
+#pragma unroll
+            for (int e = 0; e < 32; e++) {
+              const float g = fminf(v[e], lim);
+              v[e] = g / (1.0f + expf(-1.702f * g)) * (fminf(fmaxf(u[e], -lim), lim) + 1.0f);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++) v[e] = cima_gated(v[e], u[e], a.act, a.act_limit);
+          }
         }
         if (i >= p_first && i < a.p_rows) {
           const int jmax = GATED ? a.up_offset : a.q_rows;

@@ -138,11 +138,17 @@ k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_f
                    const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_dim, float eps) {
   cima_pdl_wait();
   __shared__ float vals[4][256];
+  __shared__ float rot_cos[128], rot_sin[128];
   const int row = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int head = blockIdx.x * 4 + warp;
-  if (head >= nh + nkv + nv) return;
   const int pos = row_pos[row];
+  const int half = rotary_dim >> 1;
+  if (blockIdx.x * 4 < nh + nkv) {                     // the row's angles once for the block's heads
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &rot_sin[i], &rot_cos[i]);
+    __syncthreads();
+  }
+  if (head >= nh + nkv + nv) return;
   TA* cache = cache_in;
   if (cache && pg.ring && pos + pg.ring * pg.page_size < seq_len[row_seq[row]]) cache = nullptr;
   const int slot = cache ? seq_slot[row_seq[row]] : 0;
@@ -167,14 +173,12 @@ k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_f
     for (int d = lane; d < norm_dim; d += 32) x[d] = x[d] * r * w[d];
   }
   __syncwarp();
-  const int half = rotary_dim >> 1;
   TA* dst = (cache && head >= nh) ? cache + pg.offset(slot, pos, 0, head - nh) : nullptr;
   for (int d = lane; d < hd; d += 32) {
     float y = x[d];
     if (d < rotary_dim) {
       const int i = d < half ? d : d - half;
-      float sn, cs;
-      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      const float sn = rot_sin[i], cs = rot_cos[i];
       y = d < half ? x[d] * cs - x[d + half] * sn : x[d - half] * sn + x[d] * cs;
     }
     const TA r = cima_from_f32<TA>(y);

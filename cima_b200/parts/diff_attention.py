@@ -8,6 +8,7 @@ maps over the same values and subtracts them.
     o    = rms(A_1 - lambda A_2) * (1 - diff) * sigmoid(W_g h)[head];    y = W_o o
     lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff      one number for the layer
 
+W_g's rows stand behind q | k | v in the same matrix product and pass through the convolution unchanged (taps 0, ..., 0, 1).
 Head h reads key head h // (heads / kv_heads).  The two maps run as one grouped-query attention over 2 * heads query
 heads and 2 * kv_heads key heads: key head 2 g + m is map m of key head g, the query heads are laid out so that the
 heads that read it stand together (block g holds map 1 of its heads, then map 2), and ``v_group = 2`` tells the
@@ -53,8 +54,12 @@ class DiffAttention:
         if not self.writes:
             self.nk = self.nv = 0
         self.channels = (self.nq + self.nk + self.nv) * self.hd
-        self.conv = ShortConv(ShortConvSpec(channels=self.channels, taps=self.taps), rt) if self.taps > 0 else None      # 0 taps: none
-        self.proj = self.gate = self.out = self.q_norm = self.k_norm = None
+        # the gate's rows stand behind q | k | v in the same product (up to a multiple of 8 with zero rows, so that a row of
+        # the result keeps its 16-byte alignment); through the convolution they pass with the taps 0, ..., 0, 1
+        self.gate_rows = -(-self.heads // 8) * 8
+        self.row = self.channels + self.gate_rows
+        self.conv = ShortConv(ShortConvSpec(channels=self.row, taps=self.taps), rt) if self.taps > 0 else None      # 0 taps: none
+        self.proj = self.out = self.q_norm = self.k_norm = None
         self.lam = 0.0
         self._lam_vectors = None
 
@@ -118,15 +123,19 @@ class DiffAttention:
             mats.append(self._padded(tensors[self._n(prefix, names, key)], heads, size, o))
             if self.conv is not None:
                 taps.append(self._padded(tensors[self._n(prefix, names, key, ".conv")].float(), heads, size, o))
-        self.proj = Linear(mats, None, rt)
+        g = tensors[self._n(prefix, names, "g")]
+        gate = torch.zeros((self.gate_rows, g.shape[1]), dtype=g.dtype, device=g.device)
+        gate[:self.heads] = g
+        self.proj = Linear(mats + [gate], None, rt)
         if self.conv is not None:
-            self.conv.load({"w": torch.cat(taps)}, "w")
+            through = torch.zeros((self.gate_rows, self.taps), dtype=torch.float32, device=taps[0].device)
+            through[:, -1] = 1.0
+            self.conv.load({"w": torch.cat(taps + [through])}, "w")
         self.q_norm = rt.vector(tensors[self._n(prefix, names, "q", ".norm")])
         self.k_norm = rt.vector(tensors[self._n(prefix, names, "k", ".norm")]) if self.writes else self.q_norm
         self._lam_vectors = [rt.vector(tensors[self._n(prefix, names, k)]) for k in ("lq1", "lk1", "lq2", "lk2")]
         a, b, c, d = (v.double().cpu() for v in self._lam_vectors)
         self.lam = math.exp(float((a * b).sum())) - math.exp(float((c * d).sum())) + self.diff
-        self.gate = Linear(tensors[self._n(prefix, names, "g")], None, rt)
         self.out = Linear(tensors[self._n(prefix, names, "o")], None, rt)
 
     def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
@@ -145,16 +154,16 @@ class DiffAttention:
             out[self._n(prefix, names, "k", ".norm")] = self.k_norm
         for k, v in zip(("lq1", "lk1", "lq2", "lk2"), self._lam_vectors):
             out[self._n(prefix, names, k)] = v
-        out[self._n(prefix, names, "g")] = self.gate.weight
+        out[self._n(prefix, names, "g")] = self.proj.weight[r:r + self.heads]
         out[self._n(prefix, names, "o")] = self.out.weight
         return out
 
     def nbytes(self) -> int:
-        return (self.proj.nbytes() + self.gate.nbytes() + self.out.nbytes() + (self.conv.nbytes() if self.conv is not None else 0)
+        return (self.proj.nbytes() + self.out.nbytes() + (self.conv.nbytes() if self.conv is not None else 0)
                 + (self.q_norm.numel() + self.k_norm.numel() + 4 * self.dim) * 4)
 
     def scratch_row(self) -> int:
-        return 2 * self.channels + self.nq * self.hd + self.heads * (self.vdim + 1)
+        return 2 * self.row + self.nq * self.hd + self.heads * self.vdim
 
     graph_safe = True
 
@@ -187,11 +196,11 @@ class DiffAttention:
             h = h.tensor()
         rows = h.shape[0]
         kv = cache.layer_kv(site)
-        raw = self.proj.store(h)                                      # [rows, q | k | v] (q alone where the layer reads another's)
+        raw = self.proj.store(h)                                      # [rows, q | k | v | gate] (no k, v where the layer reads another's)
         if self.conv is None:
             qkv = raw
         else:
-            qkv = rt.empty(rows, self.channels)
+            qkv = rt.empty(rows, self.row)
             conv_state = cache.state[self.conv.state_name(site)] if self.taps > 1 else None
             K_.short_conv(raw, self.conv.weight, conv_state, batch, qkv, add_input=False)
         K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq, batch.seq_slot,
@@ -201,9 +210,8 @@ class DiffAttention:
         from_cache = (not batch.prefill) or not self.writes
         K_.attention(qkv, kv, batch, att, self.nq, 2 * self.kv_heads, self.hd, s.scale, s.window, from_cache,
                      after_append=self.writes, keep_first=self.keep_first, v_group=2)
-        gate = self.gate.store(h)                                     # [rows, heads]
         o = rt.empty(rows, self.heads * self.vdim)
-        K_.diff_combine(att, gate, o, self.heads, self.rep, self.hd, self.vdim, self.lam, 1.0 - self.diff, self.eps)
+        K_.diff_combine(att, qkv[:, self.channels:self.channels + self.heads], o, self.heads, self.rep, self.hd, self.vdim, self.lam, 1.0 - self.diff, self.eps)
         return o
 
 
