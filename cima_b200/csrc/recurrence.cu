@@ -74,7 +74,12 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
   // from shared memory: every load of a stage is issued before any of them is waited for.
   constexpr int NLD = CH * DIMP / REC_THREADS;          // values of k (and of q, of g) a thread stages
   constexpr int NLV = (CH * COLS + REC_THREADS - 1) / REC_THREADS;
-  float rk[NLD], rq[NLD], rgt[DELTA ? NLD : 1], rv[NLV], rb = 0.f;
+  // They wait there as they were loaded: a conversion in front of the work would wait for the load it converts.
+  TQ rk[NLD], rq[NLD];
+  TV rv[NLV];
+  float rgt[DELTA ? NLD : 1], rb = 0.f;
+  const TQ zero_q = cima_from_f32<TQ>(0.f);
+  const TV zero_v = cima_from_f32<TV>(0.f);
   // The gate rule: k holds the gate's projection z, g its bias and decay its lower bound (the same for every token: a
   // thread stages the same channels in every round and keeps theirs).  A channel beyond the key size gets the bound 1: f = 1.
   float glow[GATE ? NLD : 1], gbias[GATE ? NLD : 1];
@@ -94,15 +99,15 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
       const int tt = idx / DIMP, i = idx - tt * DIMP;
       const size_t row = (size_t)(first + t0 + tt);
       const bool ok = tt < nt && i < dim;
-      rk[r] = ok ? cima_to_f32<TQ>(k[row * ldk + (size_t)kvh * dim + i]) : 0.f;
-      rq[r] = ok ? cima_to_f32<TQ>(q[row * ldq + (size_t)kvh * dim + i]) : 0.f;
+      rk[r] = ok ? k[row * ldk + (size_t)kvh * dim + i] : zero_q;
+      rq[r] = ok ? q[row * ldq + (size_t)kvh * dim + i] : zero_q;
       if (DELTA) rgt[r] = ok ? g[(row * heads + h) * dim + i] : 1.f;
     }
 #pragma unroll
     for (int r = 0; r < NLV; r++) {
       const int idx = threadIdx.x + r * REC_THREADS;
       const int tt = idx / COLS, cc = idx - tt * COLS;
-      rv[r] = (tt < nt && col0 + cc < vdim) ? cima_to_f32<TV>(v[(size_t)(first + t0 + tt) * ldv + (size_t)h * vdim + col0 + cc]) : 0.f;
+      rv[r] = (tt < nt && col0 + cc < vdim) ? v[(size_t)(first + t0 + tt) * ldv + (size_t)h * vdim + col0 + cc] : zero_v;
     }
     if (DELTA) rb = (int)threadIdx.x < nt ? beta[(size_t)(first + t0 + threadIdx.x) * heads + h] : 0.f;
   };
@@ -115,15 +120,16 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
     for (int r = 0; r < NLD; r++) {
       const int idx = threadIdx.x + r * REC_THREADS;
       const int tt = idx / DIMP, i = idx - tt * DIMP;
-      if (!GATE) sk[tt][i] = DELTA ? rk[r] : rec_silu(rk[r]);
-      sq[tt][i] = DELTA ? rq[r] : rec_silu(rq[r]);
+      const float fk = cima_to_f32<TQ>(rk[r]), fq = cima_to_f32<TQ>(rq[r]);
+      if (!GATE) sk[tt][i] = DELTA ? fk : rec_silu(fk);
+      sq[tt][i] = DELTA ? fq : rec_silu(fq);
       if (DELTA) sg[tt][i] = rgt[r];
-      if (GATE) sg[tt][i] = glow[r] + (1.0f - glow[r]) / (1.0f + expf(-(rk[r] + gbias[r])));
+      if (GATE) sg[tt][i] = glow[r] + (1.0f - glow[r]) / (1.0f + expf(-(fk + gbias[r])));
     }
 #pragma unroll
     for (int r = 0; r < NLV; r++) {
       const int idx = threadIdx.x + r * REC_THREADS;
-      if (idx < CH * COLS) sv[idx / COLS][idx % COLS] = CHANNEL ? rv[r] : rec_silu(rv[r]);
+      if (idx < CH * COLS) sv[idx / COLS][idx % COLS] = CHANNEL ? cima_to_f32<TV>(rv[r]) : rec_silu(cima_to_f32<TV>(rv[r]));
     }
     if (DELTA && threadIdx.x < CH) sb[threadIdx.x] = rb;
     __syncthreads();

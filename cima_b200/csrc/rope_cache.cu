@@ -130,14 +130,42 @@ k_rope_append_bf16x8(__nv_bfloat16* __restrict__ qkv, int ld, const float* __res
 // q heads and one for all k heads (no norm where the weights are null); and a row holds `nv` value heads behind its key
 // heads (nv <= nkv: neighbouring key heads share a value head), which go to the first nv heads of the pages' value
 // plane.  Sums of squares, the norm, the angle and the rotation are float32; one rounding at the store.
-template <typename TA>
+// VEC 4: a lane takes four neighbouring values at a time (one 8- or 16-byte load and store); the launch chooses it where
+// head size and row stride are multiples of 4 and the pointers are aligned, else VEC 1.
+template <typename TA> __device__ __forceinline__ void rope_load4(const TA* p, float* f);
+template <> __device__ __forceinline__ void rope_load4<float>(const float* p, float* f) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  f[0] = t.x; f[1] = t.y; f[2] = t.z; f[3] = t.w;
+}
+template <> __device__ __forceinline__ void rope_load4<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+template <typename TA> struct RopePack4;
+template <> struct RopePack4<float> {
+  float4 t;
+  __device__ __forceinline__ RopePack4(const float* f) : t(make_float4(f[0], f[1], f[2], f[3])) {}
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = t; }
+};
+template <> struct RopePack4<__nv_bfloat16> {
+  uint2 t;
+  __device__ __forceinline__ RopePack4(const float* f) {
+    *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(f[0], f[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(f[2], f[3]);
+  }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint2*>(p) = t; }
+};
+
+template <typename TA, int VEC>
 __global__ void __launch_bounds__(128)
 k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
                    const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
                    const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int nv, int hd,
                    const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_dim, float eps) {
   cima_pdl_wait();
-  __shared__ float vals[4][256];
+  __shared__ __align__(16) float vals[4][256];
   __shared__ float rot_cos[128], rot_sin[128];
   const int row = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -156,34 +184,65 @@ k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_f
   if (head >= nh + nkv) {                              // a value head: to the pages as it is
     if (!cache) return;
     TA* dst = cache + pg.offset(slot, pos, 1, head - nh - nkv);
-    for (int d = lane; d < hd; d += 32) dst[d] = u[d];
+    if (VEC == 4) {
+      for (int d = lane * 4; d < hd; d += 128) {
+        if (sizeof(TA) == 2) *reinterpret_cast<uint2*>(dst + d) = *reinterpret_cast<const uint2*>(u + d);
+        else *reinterpret_cast<float4*>(dst + d) = *reinterpret_cast<const float4*>(u + d);
+      }
+    } else {
+      for (int d = lane; d < hd; d += 32) dst[d] = u[d];
+    }
     return;
   }
   const float* w = head < nh ? q_norm : k_norm;
   float* x = vals[warp];
   float ss = 0.f;
-  for (int d = lane; d < hd; d += 32) {
-    const float v = cima_to_f32<TA>(u[d]);
-    x[d] = v;
-    if (d < norm_dim) ss = fmaf(v, v, ss);
+  if (VEC == 4) {
+    for (int d = lane * 4; d < hd; d += 128) {
+      float f[4];
+      rope_load4<TA>(u + d, f);
+      *reinterpret_cast<float4*>(x + d) = make_float4(f[0], f[1], f[2], f[3]);
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if (d + e < norm_dim) ss = fmaf(f[e], f[e], ss);
+    }
+  } else {
+    for (int d = lane; d < hd; d += 32) {
+      const float v = cima_to_f32<TA>(u[d]);
+      x[d] = v;
+      if (d < norm_dim) ss = fmaf(v, v, ss);
+    }
   }
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (VEC == 4) __syncwarp();                          // the norm's loop reads what other lanes wrote
   if (w) {
     const float r = 1.0f / sqrtf(ss / (float)norm_dim + eps);
     for (int d = lane; d < norm_dim; d += 32) x[d] = x[d] * r * w[d];
   }
   __syncwarp();
   TA* dst = (cache && head >= nh) ? cache + pg.offset(slot, pos, 0, head - nh) : nullptr;
-  for (int d = lane; d < hd; d += 32) {
+  auto turned = [&](int d) {
     float y = x[d];
     if (d < rotary_dim) {
       const int i = d < half ? d : d - half;
       const float sn = rot_sin[i], cs = rot_cos[i];
       y = d < half ? x[d] * cs - x[d + half] * sn : x[d - half] * sn + x[d] * cs;
     }
-    const TA r = cima_from_f32<TA>(y);
-    u[d] = r;
-    if (dst) dst[d] = r;
+    return y;
+  };
+  if (VEC == 4) {
+    for (int d = lane * 4; d < hd; d += 128) {
+      const float f[4] = {turned(d), turned(d + 1), turned(d + 2), turned(d + 3)};
+      const RopePack4<TA> r(f);
+      r.store(u + d);
+      if (dst) r.store(dst + d);
+    }
+  } else {
+    for (int d = lane; d < hd; d += 32) {
+      const TA r = cima_from_f32<TA>(turned(d));
+      u[d] = r;
+      if (dst) dst[d] = r;
+    }
   }
 }
 
@@ -209,8 +268,16 @@ extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_f
     const dim3 grid((unsigned)((nh + nkv + nv + 3) / 4), (unsigned)T);
     if (T > 65535) return cima_fail(CIMA_E_SIZE, "rope_append: %d rows exceed one launch of the general kernel; the caller cuts them", T);
     int rc_;
-    if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
-    else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+    const size_t bytes = dtype == CIMA_F32 ? 4 : 2;
+    const bool vec = hd % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv % (4 * bytes)) == 0 && ((uintptr_t)cache % (4 * bytes)) == 0;
+    if (vec) {
+      if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float, 4>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+      else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16, 4>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+      else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
+      return rc_ ? rc_ : cima_launch_result();
+    }
+    if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float, 1>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+    else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16, 1>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
     else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
     return rc_ ? rc_ : cima_launch_result();
   }
