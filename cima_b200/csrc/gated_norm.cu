@@ -19,25 +19,36 @@ k_scale_add_group_rmsnorm(float* __restrict__ x, const float* __restrict__ y, fl
   const int lane = threadIdx.x & 31;
   const int grp = (int)(unit % groups);
   const size_t base = (size_t)unit * n;
-  float v[32];
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < 32; j++) {
-    const int i = lane + 32 * j;
-    v[j] = 0.f;
-    if (i < n) {
-      v[j] = y ? fmaf(alpha, x[base + i], y[base + i]) : alpha * x[base + i];
-      ss = fmaf(v[j], v[j], ss);
-    }
-  }
-  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
-  const float r = 1.0f / sqrtf(ss / (float)n + eps);
+  // Every load is issued without a condition (an index beyond the group reads the group's last value, which is then not
+  // used), so that all of a lane's loads are in flight together: behind a branch each would wait for the one before it.
+  float v[32], wv[32];
   const float* wp = w + (size_t)grp * n;
 #pragma unroll
   for (int j = 0; j < 32; j++) {
+    const int i = min(lane + 32 * j, n - 1);
+    v[j] = x[base + i];
+    wv[j] = wp[i];
+  }
+  if (y) {
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = fmaf(alpha, v[j], y[base + min(lane + 32 * j, n - 1)]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = alpha * v[j];
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    if (lane + 32 * j >= n) v[j] = 0.f;
+    ss = fmaf(v[j], v[j], ss);
+  }
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float r = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
     const int i = lane + 32 * j;
     if (i < n) {
-      const float o = v[j] * r * wp[i];
+      const float o = v[j] * r * wv[j];
       x[base + i] = o;
       if (h) h[base + i] = cima_from_f32<TH>(o);
     }
