@@ -14,7 +14,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Union
 
-from .config import (ArchitectureEntry, ConfigError, GisiraxConfig, LipizenConfig, Qwen2Config, VunovikConfig, lookup_architecture, read_config_json,
+from .config import (ArchitectureEntry, ConfigError, GisiraxConfig, LipizenConfig, NetezenConfig, Qwen2Config, VunovikConfig, lookup_architecture, read_config_json,
                      register_architecture, registered_architectures)
 from .sampling import GenOptions, OptionError
 
@@ -27,6 +27,9 @@ register_architecture(ArchitectureEntry(name=GisiraxConfig.ARCHITECTURE, model_t
                                         parse_with_shapes=GisiraxConfig.from_dict))
 register_architecture(ArchitectureEntry(name=LipizenConfig.ARCHITECTURE, model_type="lipizen",
                                         parse=LipizenConfig.from_dict, spec=LipizenConfig.model_spec))
+register_architecture(ArchitectureEntry(name=NetezenConfig.ARCHITECTURE, model_type="netezen",
+                                        parse=NetezenConfig.from_dict, spec=NetezenConfig.model_spec,
+                                        parse_with_shapes=NetezenConfig.from_dict))
 
 __version__ = "0.1.0"
 
@@ -142,5 +145,5 @@ def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int 
 
 
 __all__ = ["LM", "load", "write_random_model", "eos_ids_of", "GenOptions", "OptionError", "ConfigError",
-           "Qwen2Config", "VunovikConfig", "GisiraxConfig", "LipizenConfig", "register_architecture", "registered_architectures", "lookup_architecture",
+           "Qwen2Config", "VunovikConfig", "GisiraxConfig", "LipizenConfig", "NetezenConfig", "register_architecture", "registered_architectures", "lookup_architecture",
            "read_config_json", "ArchitectureEntry"]

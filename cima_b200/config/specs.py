@@ -18,7 +18,8 @@ from typing import Any, Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str                    # "rmsnorm" | "dyt" (tanh(alpha x) * w + b: no row statistics, eps unused)
+    kind: str                    # "rmsnorm" (params["offset"] c: the stored weight w multiplies as c + w; default 0)
+                                 # | "dyt" (tanh(alpha x) * w + b: no row statistics, eps unused)
                                  # | "group_rmsnorm" (params["groups"] equal parts of a row, each divided by its own root mean square)
     size: int
     eps: float
@@ -32,7 +33,9 @@ class PositionSpec:
     rotary_dim: int              # how many leading dims of a head rotate (<= head_dim, even)
     theta: float
     # "scaling": {"factor", "low", "high", "original"}: frequencies rescaled by their wavelength (see parts/position.py);
-    # "linear": a factor every frequency is divided by
+    # "linear": a factor every frequency is divided by;
+    # "yarn": {"factor", "original", "fast", "slow"}: frequencies blended by their index between f and f / factor, sine and
+    # cosine multiplied by 0.1 ln(factor) + 1;  "interleaved": True = neighbours (2i, 2i + 1) form a pair, not (i, i + rotary_dim / 2)
     params: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -91,6 +94,8 @@ class BlockSpec:
                                  # "parallel": h = norm(x); x += mixer(conv(h)) + ffn(h)
                                  # "sandwich": x += m * post(mixer(norm(x))); x += m * post(ffn(norm(x)))
                                  # "postnorm": x = norm(a x + mixer(x)); x = norm(a x + ffn(x)), a = stream_mult
+                                 # "hyper": ``streams`` copies X_s of the stream; a sublayer reads norm(sum_s in[s] X_s) and
+                                 #          X_t <- sum_s mix[s, t] X_s + m out[t] y for all t at once, m = residual_mult
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]      # None: the layer has no feed-forward ("parallel" only)
     mixer_norm: NormSpec
@@ -108,6 +113,10 @@ class BlockSpec:
     residual_mult: float = 1.0
     # "postnorm": the factor of the stream in the sum that the norm behind a sublayer reads
     stream_mult: float = 1.0
+    # "hyper": how many copies of the stream the model carries.  With names["mixer_hc"] / names["ffn_hc"] the vectors
+    # <stem>.in, <stem>.out [streams] and the matrix <stem>.mix [streams, streams] (indexed [from, to]) of a sublayer are
+    # stored tensors; without those names they are ones and the unit matrix (one stream: x += m * sublayer(norm(x)))
+    streams: int = 1
 
 
 @dataclass(frozen=True)
@@ -137,8 +146,11 @@ class ModelSpec:
     # What a layer reads.  "residual": the stream as the layer before left it.  "depth_average": with X_0 the
     # embedding's output and X_(s+1) the stream as site s leaves it, the next site (and the final norm) reads
     # sum_(j <= s+1) a_s[j] X_j; ``depth_names[s]`` names the vector a_s (s + 2 values) of site s.
+    # "hyper": the step carries ``streams`` copies of the stream, all equal to the embedding's output at the start and
+    # summed in front of the final norm; every layer is a block of kind "hyper" with as many streams.
     stream: str = "residual"
     depth_names: Tuple[str, ...] = ()
+    streams: int = 1
 
     def describe(self) -> str:
         kinds = [f"{self.layers[i].mixer.kind}"

@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfloat16* __restrict__ cache,
                    CimaPaged pg, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int ldo,
-                   int nh, int nkv, int mtiles, float scale, int window, int n_splits, int early, float sink, int keep_first, int v_group) {
+                   int nh, int nkv, int mtiles, float scale, int window, int n_splits, int early, float sink, int keep_first, int v_group,
+                   const float* __restrict__ head_sink) {
   if (!early) cima_pdl_wait();
   constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
   constexpr int TILE = PS * ROW;                      // elements of one K or V tile
@@ -285,7 +286,8 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     }
     const int h = h0 + r;
     if (n_splits == 1) {
-      l += sink * ex2(-Ms);             // `sink` entries of score 0 without a value (0: an ordinary softmax)
+      // `sink` entries of score 0 without a value (0: an ordinary softmax), or one entry of the head's own score
+      l += (head_sink ? expf(head_sink[h]) : sink) * ex2(-Ms);
       out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     } else {
       const size_t pi = ((size_t)b * nh + h) * n_splits + split;
@@ -303,7 +305,8 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
 // L2 per split: 8 us at 32 splits.)
 __global__ void __launch_bounds__(128)
 k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seq_len,
-                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int window, int splits_launched, float sink, int keep_first) {
+                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int window, int splits_launched, float sink, int keep_first,
+                    const float* __restrict__ head_sink) {
   cima_pdl_wait();
   __shared__ float w[MAX_SPLITS];
   __shared__ float s_inv;
@@ -332,7 +335,7 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
       L += ws * l[i];
     }
     for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    L += sink * ex2(-Ms);
+    L += (head_sink ? expf(head_sink[h]) : sink) * ex2(-Ms);
     if (threadIdx.x == 0) s_inv = L > 0.f ? 1.0f / L : 0.f;
   }
   __syncthreads();
@@ -355,7 +358,7 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
 template <int HD, int PLANES>
 int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, const int* seq_slot, const int* seq_len,
                   float* part_o, float* part_ml, void* out, int ldo, int B, int nh, int nkv, float scale, int window,
-                  int n_splits, int early, float sink, int keep_first, int v_group, cudaStream_t stream) {
+                  int n_splits, int early, float sink, int keep_first, int v_group, const float* head_sink, cudaStream_t stream) {
   auto kern = k_attention_decode<HD, PLANES>;
   constexpr int STAGES = decode_stages(HD, PLANES);
   const size_t tiles = (size_t)STAGES * PLANES * PS * (HD + 8) * sizeof(__nv_bfloat16);
@@ -371,10 +374,10 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
   dim3 grid(n_splits, nkv * mtiles, B);
   { int rc_ = cima_launch(kern, dim3(grid), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, (const __nv_bfloat16*)cache, pg, seq_slot,
                                            seq_len, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, nkv, mtiles, scale,
-                                           window, n_splits, early, sink, keep_first, v_group); if (rc_) return rc_; }
+                                           window, n_splits, early, sink, keep_first, v_group, head_sink); if (rc_) return rc_; }
   int rc = cima_launch_result();
   if (rc || n_splits == 1) return rc;
-  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, seq_len, (__nv_bfloat16*)out, ldo, nh, HD, window, n_splits, sink, keep_first); if (rc_) return rc_; }
+  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, seq_len, (__nv_bfloat16*)out, ldo, nh, HD, window, n_splits, sink, keep_first, head_sink); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
@@ -388,7 +391,8 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
 extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, float* part_o,
                                      float* part_ml, void* out, int ldo, int B, int nh, int nkv, int hd, float scale,
-                                     int window, int n_splits, int early, int planes, float sink, int keep_first, int v_group, cudaStream_t stream) {
+                                     int window, int n_splits, int early, int planes, float sink, int keep_first, int v_group,
+                                     const float* head_sink, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_decode: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (page_size != PS) return cima_fail(CIMA_E_SIZE, "attention_decode: page size %d; this kernel takes 64", page_size);
@@ -399,8 +403,8 @@ extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache,
   if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
   if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
-#define CASE(H) case H: return planes == 2 ? launch_decode<H, 2>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, keep_first, v_group, stream) \
-                                          : launch_decode<H, 1>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, keep_first, v_group, stream)
+#define CASE(H) case H: return planes == 2 ? launch_decode<H, 2>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, keep_first, v_group, head_sink, stream) \
+                                          : launch_decode<H, 1>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, sink, keep_first, v_group, head_sink, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }
@@ -455,5 +459,5 @@ extern "C" int cima_attention_decode_static(const void* qkv, int ld, const void*
   float* part_o = scratch;                       // [B, nh, n_splits, hd]
   float* part_ml = scratch + cells * hd;         // [B, nh, n_splits, 2]
   return cima_attention_decode(qkv, ld, cache, table, table_width, ring, page_size, seq_slot, seq_len, part_o, part_ml,
-                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, 2, 0.f, 0, 1, stream);
+                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, 2, 0.f, 0, 1, nullptr, stream);
 }

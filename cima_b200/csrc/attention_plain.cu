@@ -9,6 +9,7 @@
 // first f positions stay visible beyond the window (at their own positions).  `v_group` neighbouring key heads share
 // one value head (1: a value head for every key head): value head = key head / v_group, and a row of the step holds
 // nkv / v_group value heads behind its key heads.
+// A head's softmax may hold one more entry without a value: `sink` entries of score 0, or exp(head_sink[h]).
 // A row's result depends only on its own sequence: same bits alone or in any batch.
 #include "common.cuh"
 
@@ -17,7 +18,8 @@ __global__ void __launch_bounds__(128)
 k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cache, CimaPaged pg,
                   const int* __restrict__ row_pos, const int* __restrict__ row_seq,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
-                  TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window, float sink, int keep_first, int v_group) {
+                  TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window, float sink, int keep_first, int v_group,
+                  const float* __restrict__ head_sink) {
   cima_pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -72,7 +74,9 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
     m = m2;
   }
   TA* op = out + (size_t)row * ldo + (size_t)h * hd;
-  l += sink * expf(-m);                 // `sink` entries of score 0 that carry no value (0: an ordinary softmax)
+  // `sink` entries of score 0 that carry no value (0: an ordinary softmax); or, with `head_sink`, one entry whose score is
+  // the head's own number (neither scaled nor attached to a value)
+  l += head_sink ? expf(head_sink[h] - m) : sink * expf(-m);
   const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < NI; i++) {
@@ -86,7 +90,8 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
                                     int table_width, int ring, int page_size, const int* row_pos,
                                     const int* row_seq, const int* seq_slot, const int* seq_first_row, void* out,
                                     int ldo, int T, int nh, int nkv, int hd, float scale, int window,
-                                    int from_cache, int planes, float sink, int keep_first, int v_group, cudaStream_t stream) {
+                                    int from_cache, int planes, float sink, int keep_first, int v_group, const float* head_sink,
+                                    cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd > 1024) return cima_fail(CIMA_E_SIZE, "attention_plain: head_dim %d is outside 1..1024", hd);
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_plain: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
@@ -98,7 +103,7 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
   dim3 grid((T + 3) / 4, nh);
 #define LAUNCH(TA, FC) { int rc_ = hd <= 256 ? LAUNCH_NI(TA, FC, 8) : LAUNCH_NI(TA, FC, 32); if (rc_) return rc_; }
 #define LAUNCH_NI(TA, FC, NI) cima_launch(k_attention_plain<TA, FC, NI>, dim3(grid), dim3(128), (size_t)(0), stream, 1, (const TA*)qkv, ld, (const TA*)cache, pg, \
-    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window, sink, keep_first, v_group)
+    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window, sink, keep_first, v_group, head_sink)
   if (dtype == CIMA_F32) { if (from_cache) LAUNCH(float, true) else LAUNCH(float, false) }
   else if (dtype == CIMA_BF16) { if (from_cache) LAUNCH(__nv_bfloat16, true) else LAUNCH(__nv_bfloat16, false) }
   else return cima_fail(CIMA_E_DTYPE, "attention_plain: dtype code %d is neither float32 nor bfloat16", dtype);

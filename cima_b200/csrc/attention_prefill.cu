@@ -65,7 +65,8 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
                     const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
                     const __nv_bfloat16* __restrict__ cache, CimaPaged pg, const int* __restrict__ seq_slot,
                     const int* __restrict__ seq_len,
-                    __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window, float sink, int keep_first, int v_group) {
+                    __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window, float sink, int keep_first, int v_group,
+                    const float* __restrict__ head_sink) {
   cima_pdl_wait();
   constexpr int ROW = HD + 8;
   constexpr int TILE = BN * ROW;
@@ -265,6 +266,8 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   cp_async_wait<0>();
 
   // `sink` entries of score 0 without a value join the denominator (0: an ordinary softmax); maxima are base-2 scores
+  // (or, with `head_sink`, one entry whose score is the head's own number)
+  if (head_sink) sink = expf(head_sink[h]);
   if (sink != 0.f) {
 #pragma unroll
     for (int r = 0; r < 2; r++) l_run[r] += sink * ex2(m_run[r] == -INFINITY ? 0.f : -m_run[r]);
@@ -283,7 +286,8 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
 template <int HD, bool FROM_CACHE>
 int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
                    const void* cache, const CimaPaged& pg, const int* seq_slot, const int* seq_len,
-                   void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window, float sink, int keep_first, int v_group, cudaStream_t stream) {
+                   void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window, float sink, int keep_first, int v_group,
+                   const float* head_sink, cudaStream_t stream) {
   if ((long long)n_tiles * nh > 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "attention_prefill: %d blocks of rows x %d heads exceed one launch", n_tiles, nh);
   auto kern = k_attention_prefill<HD, FROM_CACHE>;
   const size_t smem = (size_t)2 * 2 * BN * (HD + 8) * sizeof(__nv_bfloat16);
@@ -295,7 +299,7 @@ int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile
   }
   { int rc_ = cima_launch(kern, dim3((unsigned)n_tiles * (unsigned)nh), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
                                                         (const __nv_bfloat16*)cache, pg, seq_slot, seq_len,
-                                                        (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window, sink, keep_first, v_group); if (rc_) return rc_; }
+                                                        (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window, sink, keep_first, v_group, head_sink); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
@@ -313,11 +317,12 @@ static int prefill_checks(const char* who, const void* qkv, int ld, const void* 
 // tile_seq / tile_row0 [n_tiles]: the sequence and the first query row of each block of 64 rows.
 extern "C" int cima_attention_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
                                       const int* seq_first_row, void* out, int ldo, int T, int n_tiles, int nh, int nkv,
-                                      int hd, float scale, int window, float sink, int keep_first, int v_group, cudaStream_t stream) {
+                                      int hd, float scale, int window, float sink, int keep_first, int v_group, const float* head_sink,
+                                      cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
   if (int rc = prefill_checks("attention_prefill", qkv, ld, out, ldo, hd, nh, nkv, keep_first, v_group)) return rc;
   const CimaPaged none{nullptr, 0, 0, BN, nkv, hd};
-#define CASE(H) case H: return launch_prefill<H, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, nullptr, none, nullptr, nullptr, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, keep_first, v_group, stream)
+#define CASE(H) case H: return launch_prefill<H, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, nullptr, none, nullptr, nullptr, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, keep_first, v_group, head_sink, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }
@@ -331,14 +336,14 @@ extern "C" int cima_attention_extend(const void* qkv, int ld, const int* tile_se
                                      const int* seq_first_row, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, void* out, int ldo,
                                      int T, int n_tiles, int nh, int nkv, int hd, float scale, int window,
-                                     int planes, float sink, int keep_first, int v_group, cudaStream_t stream) {
+                                     int planes, float sink, int keep_first, int v_group, const float* head_sink, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_extend: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (int rc = prefill_checks("attention_extend", qkv, ld, out, ldo, hd, nh, nkv, keep_first, v_group)) return rc;
   if (page_size != BN) return cima_fail(CIMA_E_SIZE, "attention_extend: page size %d; this kernel takes %d", page_size, BN);
   if (!cache || !table || !seq_slot || !seq_len || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_extend: the cache (16-byte aligned), its block table, slots and lengths are needed");
   const CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
-#define CASE(H) case H: return launch_prefill<H, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, cache, pg, seq_slot, seq_len, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, keep_first, v_group, stream)
+#define CASE(H) case H: return launch_prefill<H, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, cache, pg, seq_slot, seq_len, out, ldo, T, n_tiles, nh, nkv, scale, window, sink, keep_first, v_group, head_sink, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }

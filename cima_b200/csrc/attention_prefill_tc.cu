@@ -61,6 +61,7 @@ struct AttnArgs {
   int* error_flag;
   int planes;                   // keys from the cache: 2 = a page holds keys, then values; 1 = one vector serves as both
   float sink;                   // entries of score 0 without a value that join the softmax's denominator (0: none)
+  const float* head_sink;       // or null: [nh], head h's denominator also holds exp(head_sink[h]) (instead of `sink`)
 };
 
 // Keys of a query block whose rows stand at positions p0 .. (at most p0 + 127, below len): tiles [first, last] of 64.
@@ -318,7 +319,8 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
     if (ok && n > 0) ok = mbar_wait(pv_done, (n - 1) & 1, a.error_flag, abort_flag);
     if (ok && n > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (a.sink != 0.f) l_run += a.sink * ex2(m_run == -INFINITY ? 0.f : -m_run);
+      const float sink = a.head_sink ? expf(a.head_sink[h]) : a.sink;
+      if (sink != 0.f) l_run += sink * ex2(m_run == -INFINITY ? 0.f : -m_run);
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = a.out + (size_t)(row_base + r0 + r) * a.ldo + (size_t)h * HD;
 #pragma unroll 1
@@ -357,7 +359,7 @@ struct CacheSource {              // keys and values from a layer's pages; cache
 template <int HD, bool FROM_CACHE>
 int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
                         const CacheSource& c, void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale,
-                        int window, int* error_flag, float sink, cudaStream_t stream) {
+                        int window, int* error_flag, float sink, const float* head_sink, cudaStream_t stream) {
   if ((long long)n_tiles * nh > 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d blocks of rows x %d heads exceed one launch", n_tiles, nh);
   CUtensorMap mq, mk;                                  // boxes of 128 rows (Q) and of 64 rows (K and V) by 64 columns
   // (with the keys in the cache only the queries' columns of a row are read, and the row may end there)
@@ -376,7 +378,7 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
     raised = true;
   }
   AttnArgs a{tile_seq, tile_row0, seq_first_row, c.seq_len, c.seq_slot, c.table, c.table_width, c.ring,
-             (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag, c.planes, sink};
+             (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag, c.planes, sink, head_sink};
   { int rc_ = cima_launch(k_attention_prefill_tc<HD, FROM_CACHE>, dim3((unsigned)n_tiles * (unsigned)nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
   return cima_launch_result();
 }
@@ -400,13 +402,14 @@ static int tc_checks(const char* who, const void* qkv, int ld, const void* out, 
 // error_flag: device int that a wait that ran out sets to 1 (never cleared here).
 extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
                                          const int* seq_first_row, void* out, int ldo, int T, int n_tiles, int nh,
-                                         int nkv, int hd, float scale, int window, int* error_flag, float sink, cudaStream_t stream) {
+                                         int nkv, int hd, float scale, int window, int* error_flag, float sink, const float* head_sink,
+                                         cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
   if (int rc = tc_checks("attention_prefill_tc", qkv, ld, out, ldo, nh, nkv, hd, error_flag)) return rc;
   const CacheSource none{nullptr, 0, nullptr, nullptr, nullptr, 0, 0};
   if (hd == 64)
-    return launch_attention_tc<64, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, none, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, stream);
-  return launch_attention_tc<128, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, none, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, stream);
+    return launch_attention_tc<64, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, none, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, head_sink, stream);
+  return launch_attention_tc<128, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, none, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, head_sink, stream);
 }
 
 // The same for sequences that go on: the rows of sequence s are the positions seq_len[s] - rows .. seq_len[s] - 1, and
@@ -415,7 +418,8 @@ extern "C" int cima_attention_extend_tc(const void* qkv, int ld, const int* tile
                                         const int* seq_first_row, const void* cache, long long n_pages, const int* table,
                                         int table_width, int ring, int page_size, const int* seq_slot, const int* seq_len,
                                         void* out, int ldo, int T, int n_tiles, int nh, int nkv, int hd, float scale,
-                                        int window, int* error_flag, int planes, float sink, cudaStream_t stream) {
+                                        int window, int* error_flag, int planes, float sink, const float* head_sink,
+                                        cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_extend_tc: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (int rc = tc_checks("attention_extend_tc", qkv, ld, out, ldo, nh, nkv, hd, error_flag, true)) return rc;
@@ -425,6 +429,6 @@ extern "C" int cima_attention_extend_tc(const void* qkv, int ld, const int* tile
   if (n_pages * planes * nkv * BN >= (1ll << 31)) return cima_fail(CIMA_E_SIZE, "attention_extend_tc: %lld pages exceed a tensor map's 32-bit row coordinate", n_pages);
   const CacheSource c{cache, n_pages, table, seq_slot, seq_len, table_width, ring, planes};
   if (hd == 64)
-    return launch_attention_tc<64, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, stream);
-  return launch_attention_tc<128, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, stream);
+    return launch_attention_tc<64, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, head_sink, stream);
+  return launch_attention_tc<128, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, sink, head_sink, stream);
 }

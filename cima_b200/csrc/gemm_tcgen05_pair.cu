@@ -336,10 +336,10 @@ extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float*
 // the matrix of every row tile (-1: the tile has no rows).  Epilogues 2 (gated: a matrix of Q is [gate | up],
 // q_rows = 2 * up_offset) and 3 (float32 store); out [p_rows, ldo].
 extern "C" int cima_gemm_tcgen05_pair_grouped(const void* P, const void* Q, void* out, int epi, int p_rows, int q_rows, int E,
-                                              int K, int ldo, int up_offset, int act, const int* tile_expert,
+                                              int K, int ldo, int up_offset, int act, float act_limit, const int* tile_expert,
                                               int* error_flag, cudaStream_t stream) {
   if (p_rows <= 0 || q_rows <= 0 || E <= 0) return 0;
-  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
+  if (act < 0 || act >= CIMA_GATED_COUNT) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: activation code %d is not one of 0..%d", act, CIMA_GATED_COUNT - 1);
   if (K <= 0 || K % 8) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair_grouped: K %d must be a positive multiple of 8", K);
   if (p_rows % (2 * BM)) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair_grouped: %d rows are not whole tiles of %d", p_rows, 2 * BM);
   if (((uintptr_t)P | (uintptr_t)Q) & 15) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: P and Q must be 16-byte aligned");
@@ -357,7 +357,7 @@ extern "C" int cima_gemm_tcgen05_pair_grouped(const void* P, const void* Q, void
   if (rc) return rc;
   rc = make_map(&mq, Q, (long long)E * q_rows, K, K, BN / 2);
   if (rc) return rc;
-  PairArgs a{p_rows, q_rows, K, up_offset, nullptr, out, ldo, error_flag, act, tile_expert, q_rows};
+  PairArgs a{p_rows, q_rows, K, up_offset, nullptr, out, ldo, error_flag, act, tile_expert, q_rows, act_limit};
   if (epi == EPI_SWIGLU) return launch<BN, 6, EPI_SWIGLU>(mp, mq, a, p_tiles, tiles_q, stream);
   return launch<BN, 6, EPI_STORE_F32>(mp, mq, a, p_tiles, tiles_q, stream);
 }

@@ -7,6 +7,7 @@
 //
 // head_linear: the same small matrix product for every head,
 //   out[t, h, n] = sum_k a[t, h, k] * w[h, n, k]        a: [T, heads, K] in rows of lda; out: [T, heads, N] in rows of ldo
+// (a head of a row may be wider than K or N: `ha` and `ho` values lie between one head's start and the next in a and out)
 // which moves a query into the latents' space (w = the key projection's head, transposed) and an attention
 // result out of it (w = the value projection's head).  FFMA with one float32 accumulator per output in ascending
 // k: the same bits for a row whatever comes with it.  It serves the 32-bit path at every size and the
@@ -51,15 +52,16 @@ extern "C" int cima_latent_append(const void* raw, int dtype, int ld, const floa
 // ------------------------------------------------------------------------------------------- head_linear
 template <typename TA>
 __global__ void __launch_bounds__(256)
-k_head_linear(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict__ out, int M, int N, int K, int lda, int ldo) {
+k_head_linear(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict__ out, int M, int N, int K, int lda, int ldo,
+              int ha, int ho) {
   cima_pdl_wait();
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int head = blockIdx.z;
-  A += (size_t)head * K;
+  A += (size_t)head * ha;
   W += (size_t)head * N * K;
-  out += (size_t)head * N;
+  out += (size_t)head * ho;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   float acc[4][4];
@@ -138,7 +140,7 @@ struct LatentJob {
 template <typename TA>
 __global__ void __launch_bounds__(32 * HL_FEW_ROWS)
 k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict__ out, int M, int N, int K, int lda, int ldo,
-                  int vec, LatentJob<TA> job) {
+                  int ha, int ho, int vec, LatentJob<TA> job) {
   extern __shared__ __align__(16) float a_sh[];         // [M][Kp], Kp = K rounded up to 4
   const int Kp = (K + 3) & ~3;
   const int head = blockIdx.y;
@@ -175,7 +177,7 @@ k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __rest
     for (int q = 0; q < HL_FEW_K; q++) w[q] = q < kn0 ? cima_to_f32<TA>(wr[q]) : 0.f;
   }
   cima_pdl_wait();
-  A += (size_t)head * K;
+  A += (size_t)head * ha;
   for (int e = threadIdx.x; e < M * Kp; e += blockDim.x) {
     const int r = e / Kp, k = e - r * Kp;
     a_sh[e] = k < K ? cima_to_f32<TA>(A[(size_t)r * lda + k]) : 0.f;
@@ -211,20 +213,20 @@ k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __rest
       }
     }
   }
-  if (live) out[(size_t)m * ldo + (size_t)head * N + n] = cima_from_f32<TA>(acc);
+  if (live) out[(size_t)m * ldo + (size_t)head * ho + n] = cima_from_f32<TA>(acc);
 }
 
 // a [M, heads, K] in rows of lda, w [heads, N, K] contiguous, out [M, heads, N] in rows of ldo; all of `dtype`.
 // raw (may be null) ... R: the arguments of cima_latent_append for the same M rows, done by the same launch; only for
 // the few rows of a decode step (M <= 8).
 static int head_linear_impl(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
-                            int ldo, const void* raw, int ld_raw, const float* g, float eps, void* cache, const int* table,
+                            int ldo, int ha, int ho, const void* raw, int ld_raw, const float* g, float eps, void* cache, const int* table,
                             int table_width, int ring, int page_size, const int* row_pos, const int* row_seq,
                             const int* seq_slot, int R, cudaStream_t stream);
 
 extern "C" int cima_head_linear(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
-                                int ldo, cudaStream_t stream) {
-  return head_linear_impl(a, w, out, dtype, M, heads, N, K, lda, ldo, nullptr, 0, nullptr, 0.f, nullptr, nullptr, 0, 0, 0,
+                                int ldo, int ha, int ho, cudaStream_t stream) {
+  return head_linear_impl(a, w, out, dtype, M, heads, N, K, lda, ldo, ha, ho, nullptr, 0, nullptr, 0.f, nullptr, nullptr, 0, 0, 0,
                           nullptr, nullptr, nullptr, 0, stream);
 }
 
@@ -236,17 +238,18 @@ extern "C" int cima_head_linear_append(const void* a, const void* w, void* out, 
     return cima_fail(CIMA_E_SIZE, "head_linear_append: %d rows of %d values; the launch that also appends takes at most %d rows", M, K, HL_FEW_ROWS);
   if (!raw || !g || !cache || !table || R <= 0 || ld_raw < R)
     return cima_fail(CIMA_E_ARG, "head_linear_append: the compressed rows (%d values in rows of %d), the norm's weight, the pages and their table are needed", R, ld_raw);
-  return head_linear_impl(a, w, out, dtype, M, heads, N, K, lda, ldo, raw, ld_raw, g, eps, cache, table, table_width, ring,
+  return head_linear_impl(a, w, out, dtype, M, heads, N, K, lda, ldo, K, N, raw, ld_raw, g, eps, cache, table, table_width, ring,
                           page_size, row_pos, row_seq, seq_slot, R, stream);
 }
 
 static int head_linear_impl(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
-                            int ldo, const void* raw, int ld_raw, const float* g, float eps, void* cache, const int* table,
+                            int ldo, int ha, int ho, const void* raw, int ld_raw, const float* g, float eps, void* cache, const int* table,
                             int table_width, int ring, int page_size, const int* row_pos, const int* row_seq,
                             const int* seq_slot, int R, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (heads <= 0 || N <= 0 || K <= 0) return cima_fail(CIMA_E_SIZE, "head_linear: %d heads, N %d and K %d must be positive", heads, N, K);
-  if (lda < heads * K || ldo < heads * N) return cima_fail(CIMA_E_SIZE, "head_linear: rows of (%d, %d) do not hold %d heads of (%d, %d)", lda, ldo, heads, K, N);
+  if (ha < K || ho < N || lda < (heads - 1) * ha + K || ldo < (heads - 1) * ho + N)
+    return cima_fail(CIMA_E_SIZE, "head_linear: rows of (%d, %d) do not hold %d heads of (%d, %d) at every (%d, %d) values", lda, ldo, heads, K, N, ha, ho);
   if (heads > 65535 || (M + 63) / 64 > 65535) return cima_fail(CIMA_E_SIZE, "head_linear: %d heads / %d rows exceed one launch", heads, M);
   int rc;
   if (M <= HL_FEW_ROWS && (size_t)M * (K + 3) * 4 <= 48 * 1024) {
@@ -255,18 +258,135 @@ static int head_linear_impl(const void* a, const void* w, void* out, int dtype, 
     const size_t smem = (size_t)M * ((K + 3) & ~3) * sizeof(float);
     const int esz = dtype == CIMA_F32 ? 4 : 2;
     const int vec = (((uintptr_t)w & 15) == 0 && ((size_t)K * esz) % 16 == 0) ? 1 : 0;      // every row of w starts on 16 bytes
-    if (dtype == CIMA_F32) rc = cima_launch(k_head_linear_few<float>, grid, dim3(32 * M), smem, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo, vec,
+    if (dtype == CIMA_F32) rc = cima_launch(k_head_linear_few<float>, grid, dim3(32 * M), smem, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo, ha, ho, vec,
                                                 LatentJob<float>{(const float*)raw, ld_raw, g, eps, (float*)cache, pg, row_pos, row_seq, seq_slot, R});
-    else if (dtype == CIMA_BF16) rc = cima_launch(k_head_linear_few<__nv_bfloat16>, grid, dim3(32 * M), smem, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo, vec,
+    else if (dtype == CIMA_BF16) rc = cima_launch(k_head_linear_few<__nv_bfloat16>, grid, dim3(32 * M), smem, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo, ha, ho, vec,
                                                   LatentJob<__nv_bfloat16>{(const __nv_bfloat16*)raw, ld_raw, g, eps, (__nv_bfloat16*)cache, pg, row_pos, row_seq, seq_slot, R});
     else return cima_fail(CIMA_E_DTYPE, "head_linear: dtype code %d is neither float32 nor bfloat16", dtype);
   } else if (dtype == CIMA_BF16) {
     const dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
-    rc = cima_launch(k_head_linear<__nv_bfloat16>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo);
+    rc = cima_launch(k_head_linear<__nv_bfloat16>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo, ha, ho);
   } else if (dtype == CIMA_F32) {
     const dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
-    rc = cima_launch(k_head_linear<float>, grid, dim3(256), (size_t)0, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo);
+    rc = cima_launch(k_head_linear<float>, grid, dim3(256), (size_t)0, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo, ha, ho);
   } else return cima_fail(CIMA_E_DTYPE, "head_linear: dtype code %d is neither float32 nor bfloat16", dtype);
   if (rc) return rc;
   return cima_launch_result();
+}
+
+// ------------------------------------------------------------------------------------------- latent_prepare, rope_rows
+// latent_prepare: a row of a latent attention's first product is [first | R | rot]: with cq, the first part is a query
+// latent, cq = rms(part) * q_norm; c = rms(second part) * c_norm; the third part is rotated at the row's position.
+// [c | rotated part] goes to the row's place in the one-plane pages (heads of R + rot values) and, with `step`, twice
+// into a row of the step's own buffer (as key and as value of a prompt's attention).  A block a row: warp 0 norms the
+// query latent, warp 1 the latent, warp 2 rotates; sums of squares by a shuffle tree, float32 throughout, one rounding
+// at each store.  Pairs: (2i, 2i + 1) where `interleaved`, else (i, i + rot / 2); sine and cosine times `amp`.
+template <typename TA>
+__global__ void __launch_bounds__(96)
+k_latent_prepare(const TA* __restrict__ ql, int ld, int first, const float* __restrict__ q_norm, TA* __restrict__ cq, int q_rank,
+                 const float* __restrict__ c_norm, float eps, int R, int rot, const float* __restrict__ inv_freq, float amp,
+                 int interleaved, TA* __restrict__ cache_in, CimaPaged pg, const int* __restrict__ row_pos,
+                 const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
+                 TA* __restrict__ step, int step_ld, int step_col) {
+  cima_pdl_wait();
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const TA* r = ql + (size_t)row * ld;
+  const int pos = row_pos[row];
+  TA* cache = cache_in;
+  // in a ring of pages a position whose place a later position of the same step takes is not written at all
+  if (cache && pg.ring && pos + pg.ring * pg.page_size < seq_len[row_seq[row]]) cache = nullptr;
+  TA* dst = cache ? cache + pg.offset(seq_slot[row_seq[row]], pos, 0, 0) : nullptr;
+  TA* s1 = step ? step + (size_t)row * step_ld + step_col : nullptr;
+  TA* s2 = s1 ? s1 + R + rot : nullptr;
+  if (warp == 0) {
+    if (!cq) return;
+    float ss = 0.f;
+    for (int i = lane; i < q_rank; i += 32) { const float v = cima_to_f32<TA>(r[i]); ss = fmaf(v, v, ss); }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    TA* out = cq + (size_t)row * q_rank;
+    for (int i = lane; i < q_rank; i += 32) out[i] = cima_from_f32<TA>(cima_to_f32<TA>(r[i]) * inv * q_norm[i]);
+  } else if (warp == 1) {
+    const TA* c = r + first;
+    float ss = 0.f;
+    for (int i = lane; i < R; i += 32) { const float v = cima_to_f32<TA>(c[i]); ss = fmaf(v, v, ss); }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)R + eps);
+    for (int i = lane; i < R; i += 32) {
+      const TA v = cima_from_f32<TA>(cima_to_f32<TA>(c[i]) * inv * c_norm[i]);
+      if (dst) dst[i] = v;
+      if (s1) { s1[i] = v; s2[i] = v; }
+    }
+  } else {
+    const TA* k = r + first + R;
+    const int half = rot >> 1;
+    for (int i = lane; i < half; i += 32) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      sn *= amp; cs *= amp;
+      const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+      const float a = cima_to_f32<TA>(k[ia]), b = cima_to_f32<TA>(k[ib]);
+      const TA ra = cima_from_f32<TA>(a * cs - b * sn), rb = cima_from_f32<TA>(b * cs + a * sn);
+      if (dst) { dst[R + ia] = ra; dst[R + ib] = rb; }
+      if (s1) { s1[R + ia] = ra; s1[R + ib] = rb; s2[R + ia] = ra; s2[R + ib] = rb; }
+    }
+  }
+}
+
+extern "C" int cima_latent_prepare(const void* ql, int dtype, int ld, int first, const float* q_norm, void* cq, int q_rank,
+                                   const float* c_norm, float eps, int R, int rot, const float* inv_freq, float amp, int interleaved,
+                                   void* cache, const int* table, int table_width, int ring, int page_size, const int* row_pos,
+                                   const int* row_seq, const int* seq_slot, const int* seq_len, void* step, int step_ld, int step_col,
+                                   int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (R <= 0 || rot < 0 || (rot & 1) || first < 0 || ld < first + R + rot)
+    return cima_fail(CIMA_E_SIZE, "latent_prepare: rows of %d values do not hold %d + %d + an even %d", ld, first, R, rot);
+  if (cq && (q_rank <= 0 || q_rank > first || !q_norm)) return cima_fail(CIMA_E_ARG, "latent_prepare: a query latent of %d values within the first %d, with its norm's weight, is needed", q_rank, first);
+  if (!c_norm || (rot && !inv_freq)) return cima_fail(CIMA_E_ARG, "latent_prepare: the latent norm's weight and the rotation's frequencies are needed");
+  if (!cache || !table || !seq_len) return cima_fail(CIMA_E_ARG, "latent_prepare: the layer's pages, their block table and the sequences' lengths are needed");
+  if (step && step_ld < step_col + 2 * (R + rot)) return cima_fail(CIMA_E_SIZE, "latent_prepare: the step's rows of %d values do not hold two copies from column %d on", step_ld, step_col);
+  CimaPaged pg{table, table_width, ring, page_size, 1, R + rot, 1};
+  int rc;
+  if (dtype == CIMA_F32) rc = cima_launch(k_latent_prepare<float>, dim3(T), dim3(96), (size_t)0, stream, 1, (const float*)ql, ld, first, q_norm, (float*)cq, q_rank, c_norm, eps, R, rot, inv_freq, amp, interleaved, (float*)cache, pg, row_pos, row_seq, seq_slot, seq_len, (float*)step, step_ld, step_col);
+  else if (dtype == CIMA_BF16) rc = cima_launch(k_latent_prepare<__nv_bfloat16>, dim3(T), dim3(96), (size_t)0, stream, 1, (const __nv_bfloat16*)ql, ld, first, q_norm, (__nv_bfloat16*)cq, q_rank, c_norm, eps, R, rot, inv_freq, amp, interleaved, (__nv_bfloat16*)cache, pg, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)step, step_ld, step_col);
+  else return cima_fail(CIMA_E_DTYPE, "latent_prepare: dtype code %d is neither float32 nor bfloat16", dtype);
+  return rc ? rc : cima_launch_result();
+}
+
+// rope_rows: out[t, h * o_head + o_off + j] = the j-th of `rot` values q[t, h * q_head + q_off + ...] rotated at row t's position.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+k_rope_rows(const TA* __restrict__ q, int ldq, int q_off, int q_head, TA* __restrict__ out, int ldo, int o_off, int o_head, int heads,
+            int rot, const float* __restrict__ inv_freq, float amp, int interleaved, const int* __restrict__ row_pos) {
+  cima_pdl_wait();
+  const int row = blockIdx.x;
+  const int half = rot >> 1;
+  const float pos = (float)row_pos[row];
+  for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    float sn, cs;
+    sincosf(pos * inv_freq[i], &sn, &cs);
+    sn *= amp; cs *= amp;
+    const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+    const TA* src = q + (size_t)row * ldq + (size_t)h * q_head + q_off;
+    TA* dst = out + (size_t)row * ldo + (size_t)h * o_head + o_off;
+    const float a = cima_to_f32<TA>(src[ia]), b = cima_to_f32<TA>(src[ib]);
+    dst[ia] = cima_from_f32<TA>(a * cs - b * sn);
+    dst[ib] = cima_from_f32<TA>(b * cs + a * sn);
+  }
+}
+
+extern "C" int cima_rope_rows(const void* q, int dtype, int ldq, int q_off, int q_head, void* out, int ldo, int o_off, int o_head,
+                              int heads, int rot, const float* inv_freq, float amp, int interleaved, const int* row_pos, int T,
+                              cudaStream_t stream) {
+  if (T <= 0 || rot == 0) return 0;
+  if (heads <= 0 || rot < 0 || (rot & 1) || q_off < 0 || o_off < 0 || ldq < (heads - 1) * q_head + q_off + rot || ldo < (heads - 1) * o_head + o_off + rot)
+    return cima_fail(CIMA_E_SIZE, "rope_rows: %d heads of %d rotating values do not fit rows of (%d, %d)", heads, rot, ldq, ldo);
+  if (!inv_freq || !row_pos) return cima_fail(CIMA_E_ARG, "rope_rows: the frequencies and the rows' positions are needed");
+  int rc;
+  if (dtype == CIMA_F32) rc = cima_launch(k_rope_rows<float>, dim3(T), dim3(128), (size_t)0, stream, 1, (const float*)q, ldq, q_off, q_head, (float*)out, ldo, o_off, o_head, heads, rot, inv_freq, amp, interleaved, row_pos);
+  else if (dtype == CIMA_BF16) rc = cima_launch(k_rope_rows<__nv_bfloat16>, dim3(T), dim3(128), (size_t)0, stream, 1, (const __nv_bfloat16*)q, ldq, q_off, q_head, (__nv_bfloat16*)out, ldo, o_off, o_head, heads, rot, inv_freq, amp, interleaved, row_pos);
+  else return cima_fail(CIMA_E_DTYPE, "rope_rows: dtype code %d is neither float32 nor bfloat16", dtype);
+  return rc ? rc : cima_launch_result();
 }

@@ -1,6 +1,7 @@
 // A routed feed-forward (mixture of experts) in five launches, none of which needs a number on the host:
-//   moe_route     scores s = sigmoid(logits); groups of neighbouring experts scored by their two best; the best `keep`
-//                 groups stay; the `top` best experts among them; weights s / (sum s + 1e-20) * scale        (float32)
+//   moe_route     scores s = sigmoid(logits) (or softmax over the experts); groups of neighbouring experts scored by their two
+//                 best; the best `keep` groups stay; the `top` best experts among them; weights s / (sum s + 1e-20) * scale
+//                 (float32).  With a correction vector c the comparisons use s + c, the weights s.
 //   moe_sort      the (row, choice) pairs ordered by expert: offsets of every expert's pairs and of its row tiles
 //   moe_gemm 0    z[i] = act(W_gate[e] h[row]) * (W_up[e] h[row])      for the sorted pairs i (a tile = 32 pairs of one expert)
 //   moe_gemm 1    y[pair] = W_down[e] z[i]                             float32, back at the pair's own place
@@ -47,10 +48,11 @@ __device__ __forceinline__ void moe_sort_block(const int* idx, int P, int E, int
 // One thread a row.  With at most ROUTE_SMEM_EXPERTS experts the row's scores live in shared memory (a decode step's
 // few rows would otherwise walk dependent loads from global memory); with more they stay in the caller's buffer.
 constexpr int ROUTE_THREADS = 64, ROUTE_SMEM_EXPERTS = 128;
-__device__ __forceinline__ void moe_route_row(float* scores, float* local, int row, int E, int top, int groups, int keep, float scale,
-                                              int* idx, float* wgt);
+__device__ __forceinline__ void moe_route_row(float* scores, float* local, int row, int E, int ld, int top, int groups, int keep, float scale,
+                                              int softmax, const float* corr, int* idx, float* wgt);
 __global__ void __launch_bounds__(ROUTE_THREADS)
-k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int keep, float scale, int* __restrict__ idx,
+k_moe_route(float* __restrict__ scores, int T, int E, int ld, int top, int groups, int keep, float scale, int softmax,
+            const float* __restrict__ corr, int* __restrict__ idx,
             float* __restrict__ wgt, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ perm) {
   cima_pdl_wait();
   cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
@@ -58,41 +60,54 @@ k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int k
   __shared__ int cnt[MOE_MAX_EXPERTS];
   __shared__ int off[MOE_MAX_EXPERTS + 1];
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row < T) moe_route_row(scores, local, row, E, top, groups, keep, scale, idx, wgt);
+  if (row < T) moe_route_row(scores, local, row, E, ld, top, groups, keep, scale, softmax, corr, idx, wgt);
   if (offsets) {             // a step of one block's rows: the pairs are ordered by expert here, which saves moe_sort's launch
     __syncthreads();
     moe_sort_block(idx, T * top, E, offsets, tiles, perm, cnt, off);
   }
 }
 
-__device__ __forceinline__ void moe_route_row(float* scores, float* local, int row, int E, int top, int groups, int keep, float scale,
-                                              int* idx, float* wgt) {
-  float* s = E <= ROUTE_SMEM_EXPERTS ? local + threadIdx.x * (E + 1) : scores + (size_t)row * E;
-  const float* z = scores + (size_t)row * E;
+__device__ __forceinline__ void moe_route_row(float* scores, float* local, int row, int E, int ld, int top, int groups, int keep, float scale,
+                                              int softmax, const float* corr, int* idx, float* wgt) {
+  float* s = E <= ROUTE_SMEM_EXPERTS ? local + threadIdx.x * (E + 1) : scores + (size_t)row * ld;
+  const float* z = scores + (size_t)row * ld;
+  float zmax = -INFINITY;
+  if (softmax)
+    for (int e = 0; e < E; e++) zmax = fmaxf(zmax, z[e]);
+  float den = 0.f;
   for (int e0 = 0; e0 < E; e0 += 8) {                     // eight logits requested before any is waited for
     float t[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) t[j] = e0 + j < E ? z[e0 + j] : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++)
-      if (e0 + j < E) s[e0 + j] = 1.0f / (1.0f + expf(-t[j]));
+      if (e0 + j < E) {
+        const float v = softmax ? expf(t[j] - zmax) : 1.0f / (1.0f + expf(-t[j]));
+        s[e0 + j] = v;
+        den += v;
+      }
   }
+  if (softmax) {
+    const float inv = 1.0f / den;
+    for (int e = 0; e < E; e++) s[e] *= inv;
+  }
+  // an expert is compared by s + its correction and weighted by s; a taken one is marked with -inf
   const int per = E / groups;
   unsigned long long kept = ~0ull;
   if (keep < groups) {
     kept = 0ull;
     for (int c = 0; c < keep; c++) {
       int best = -1;
-      float bs = -1.f;
+      float bs = -INFINITY;
       for (int gi = 0; gi < groups; gi++) {
         if ((kept >> gi) & 1ull) continue;
-        float a1 = -1.f, a2 = -1.f;                        // the group's two largest scores
+        float a1 = -INFINITY, a2 = -INFINITY;              // the group's two largest scores
         for (int e = gi * per; e < (gi + 1) * per; e++) {
-          const float v = s[e];
+          const float v = s[e] + (corr ? corr[e] : 0.f);
           if (v > a1) { a2 = a1; a1 = v; } else if (v > a2) a2 = v;
         }
         const float sc = per >= 2 ? a1 + a2 : a1;
-        if (sc > bs) { bs = sc; best = gi; }
+        if (sc > bs || best < 0) { bs = sc; best = gi; }
       }
       kept |= 1ull << best;
     }
@@ -100,18 +115,21 @@ __device__ __forceinline__ void moe_route_row(float* scores, float* local, int r
   float sum = 0.f;
   for (int c = 0; c < top; c++) {
     int best = -1;
-    float bs = -1.f;
+    float bs = -INFINITY;
     for (int gi = 0; gi < groups; gi++) {
       if (!((kept >> gi) & 1ull)) continue;
       for (int e = gi * per; e < (gi + 1) * per; e++) {
-        const float v = s[e];
-        if (v > bs) { bs = v; best = e; }
+        const float raw = s[e];
+        if (raw == -INFINITY) continue;
+        const float v = raw + (corr ? corr[e] : 0.f);
+        if (v > bs || best < 0) { bs = v; best = e; }
       }
     }
+    const float w = s[best];
     idx[(size_t)row * top + c] = best;
-    wgt[(size_t)row * top + c] = bs;
-    sum += bs;
-    s[best] = -2.f;                                        // taken
+    wgt[(size_t)row * top + c] = w;
+    sum += w;
+    s[best] = -INFINITY;                                   // taken
   }
   const float f = scale / (sum + 1e-20f);
   for (int c = 0; c < top; c++) wgt[(size_t)row * top + c] *= f;
@@ -133,7 +151,7 @@ k_moe_sort(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets,
 template <typename TA, typename TW, int MODE>
 __global__ void __launch_bounds__(256)
 k_moe_gemm(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __restrict__ out, const int* __restrict__ offsets,
-           const int* __restrict__ tiles, const int* __restrict__ perm, int E, int top, int N, int K, int act) {
+           const int* __restrict__ tiles, const int* __restrict__ perm, int E, int top, int N, int K, int act, float limit) {
   cima_pdl_wait();
   __shared__ float As[BK][BM + 1];
   __shared__ float Bs[MODE == 0 ? 2 : 1][BK][BN + 1];
@@ -207,7 +225,7 @@ k_moe_gemm(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __
       if (MODE == 0) {
         // the gate is rounded to the activations' dtype before its activation, as a stored projection would be
         const float gt = cima_to_f32<TA>(cima_from_f32<TA>(acc[i][j])), up = cima_to_f32<TA>(cima_from_f32<TA>(acc2[i][j]));
-        reinterpret_cast<TA*>(out)[(size_t)(i0 + r) * N + c] = cima_from_f32<TA>(cima_gate_act(gt, act) * up);
+        reinterpret_cast<TA*>(out)[(size_t)(i0 + r) * N + c] = cima_from_f32<TA>(cima_gated(gt, up, act, limit));
       } else {
         reinterpret_cast<float*>(out)[(size_t)perm[i0 + r] * N + c] = acc[i][j];
       }
@@ -288,7 +306,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
           const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ perm, int E, int top, int N,
-          int K, int act) {
+          int K, int act, float limit) {
   cima_pdl_wait();
   __shared__ int s_row[BM];
   __shared__ int s_e, s_i0, s_n;
@@ -371,7 +389,7 @@ k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __r
           if (MODE == 0) {
             // gate and up are rounded to bfloat16 before the activation, as stored projections would be
             const float gt = __bfloat162float(__float2bfloat16_rn(acc[2 * f][r])), uv = __bfloat162float(__float2bfloat16_rn(acc[2 * f + 1][r]));
-            reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(i0 + r0 + r) * N + n + 8 * f] = __float2bfloat16_rn(cima_gate_act(gt, act) * uv);
+            reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(i0 + r0 + r) * N + n + 8 * f] = __float2bfloat16_rn(cima_gated(gt, uv, act, limit));
           } else {
             reinterpret_cast<float*>(out)[(size_t)perm[i0 + r0 + r] * N + n + 8 * f] = acc[f][r];
           }
@@ -384,15 +402,17 @@ k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __r
 
 // scores [T, E] float32: the router's logits on entry, scratch afterwards.  idx [T, top] int32, wgt [T, top] float32.
 // offsets, tiles, perm: null, or (at most 64 rows) the outputs of moe_sort, made by the same launch.
-extern "C" int cima_moe_route(float* scores, int T, int E, int top, int groups, int keep, float scale, int* idx, float* wgt,
+extern "C" int cima_moe_route(float* scores, int T, int E, int ld, int top, int groups, int keep, float scale, int softmax,
+                              const float* correction, int* idx, float* wgt,
                               int* offsets, int* tiles, int* perm, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (ld < E) return cima_fail(CIMA_E_SIZE, "moe_route: rows of %d scores hold no %d experts", ld, E);
   if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || groups > 64 || E % groups || keep <= 0 || keep > groups)
     return cima_fail(CIMA_E_SIZE, "moe_route: %d experts in %d groups of which %d stay are not accepted (at most %d experts in at most 64 equal groups)", E, groups, keep, MOE_MAX_EXPERTS);
   if (top <= 0 || top > keep * (E / groups)) return cima_fail(CIMA_E_SIZE, "moe_route: %d choices among %d experts that stay", top, keep * (E / groups));
   if ((offsets || tiles || perm) && (!offsets || !tiles || !perm || T > ROUTE_THREADS))
     return cima_fail(CIMA_E_ARG, "moe_route: ordering the pairs here takes offsets, tiles and perm and at most %d rows (%d given)", ROUTE_THREADS, T);
-  int rc = cima_launch(k_moe_route, dim3((T + ROUTE_THREADS - 1) / ROUTE_THREADS), dim3(ROUTE_THREADS), (size_t)0, stream, 1, scores, T, E, top, groups, keep, scale, idx, wgt, offsets, tiles, perm);
+  int rc = cima_launch(k_moe_route, dim3((T + ROUTE_THREADS - 1) / ROUTE_THREADS), dim3(ROUTE_THREADS), (size_t)0, stream, 1, scores, T, E, ld, top, groups, keep, scale, softmax, correction, idx, wgt, offsets, tiles, perm);
   return rc ? rc : cima_launch_result();
 }
 
@@ -405,16 +425,16 @@ extern "C" int cima_moe_sort(const int* idx, int P, int E, int* offsets, int* ti
 
 // mode 0: a [T, lda] (adtype), w [E, 2 N, K] (wdtype), out [P, N] (adtype); mode 1: a [P, lda], w [E, N, K], out [P, N] float32.
 extern "C" int cima_moe_gemm(const void* a, int adtype, int lda, const void* w, int wdtype, void* out, const int* offsets,
-                             const int* tiles, const int* perm, int P, int E, int top, int N, int K, int mode, int act,
+                             const int* tiles, const int* perm, int P, int E, int top, int N, int K, int mode, int act, float limit,
                              cudaStream_t stream) {
   if (P <= 0) return 0;
   if (N <= 0 || K <= 0 || E <= 0 || top <= 0) return cima_fail(CIMA_E_SIZE, "moe_gemm: sizes must be positive");
   if (mode != 0 && mode != 1) return cima_fail(CIMA_E_ARG, "moe_gemm: mode %d is neither 0 (gate | up) nor 1 (down)", mode);
-  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "moe_gemm: activation code %d is unknown", act);
+  if (act < 0 || act >= CIMA_GATED_COUNT) return cima_fail(CIMA_E_ARG, "moe_gemm: activation code %d is unknown", act);
   const dim3 grid((unsigned)((P + BM - 1) / BM + E), (unsigned)((N + BN - 1) / BN));
   if (grid.y > 65535) return cima_fail(CIMA_E_SIZE, "moe_gemm: %d outputs exceed one launch", N);
   int rc;
-#define RUN(TA, TW, M) rc = cima_launch(k_moe_gemm<TA, TW, M>, grid, dim3(256), (size_t)0, stream, 1, (const TA*)a, lda, (const TW*)w, out, offsets, tiles, perm, E, top, N, K, act)
+#define RUN(TA, TW, M) rc = cima_launch(k_moe_gemm<TA, TW, M>, grid, dim3(256), (size_t)0, stream, 1, (const TA*)a, lda, (const TW*)w, out, offsets, tiles, perm, E, top, N, K, act, limit)
   if (adtype == CIMA_F32 && wdtype == CIMA_F32) { if (mode == 0) RUN(float, float, 0); else RUN(float, float, 1); }
   else if (adtype == CIMA_BF16 && wdtype == CIMA_BF16) { if (mode == 0) RUN(__nv_bfloat16, __nv_bfloat16, 0); else RUN(__nv_bfloat16, __nv_bfloat16, 1); }
   else if (adtype == CIMA_BF16 && wdtype == CIMA_F32) { if (mode == 0) RUN(__nv_bfloat16, float, 0); else RUN(__nv_bfloat16, float, 1); }
@@ -450,17 +470,17 @@ extern "C" int cima_moe_gather_rows(const void* src, const int* pos, void* dst, 
 
 // The products of moe_gemm for few pairs, bfloat16 activations and weights, K a multiple of 8, 16-byte aligned rows.
 extern "C" int cima_moe_few(const void* a, int lda, const void* w, void* out, const int* offsets, const int* tiles,
-                            const int* perm, int P, int E, int top, int N, int K, int mode, int act, cudaStream_t stream) {
+                            const int* perm, int P, int E, int top, int N, int K, int mode, int act, float limit, cudaStream_t stream) {
   if (P <= 0) return 0;
   if (N <= 0 || K <= 0 || K % 8 || lda % 8 || E <= 0 || top <= 0 || (((uintptr_t)a | (uintptr_t)w) & 15))
     return cima_fail(CIMA_E_SIZE, "moe_few: K %d and the row stride %d must be multiples of 8 and the operands 16-byte aligned", K, lda);
   if (mode != 0 && mode != 1) return cima_fail(CIMA_E_ARG, "moe_few: mode %d is neither 0 (gate | up) nor 1 (down)", mode);
-  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "moe_few: activation code %d is unknown", act);
+  if (act < 0 || act >= CIMA_GATED_COUNT) return cima_fail(CIMA_E_ARG, "moe_few: activation code %d is unknown", act);
   const int per_block = 8 * (mode == 0 ? FEW_ROWS / 2 : FEW_ROWS);          // features of a block: its 8 warps' 
   const dim3 grid((unsigned)((P + BM - 1) / BM + E), (unsigned)((N + per_block - 1) / per_block));
   if (grid.y > 65535) return cima_fail(CIMA_E_SIZE, "moe_few: %d outputs exceed one launch", N);
   int rc;
-  if (mode == 0) rc = cima_launch(k_moe_few<0>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act);
-  else rc = cima_launch(k_moe_few<1>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act);
+  if (mode == 0) rc = cima_launch(k_moe_few<0>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act, limit);
+  else rc = cima_launch(k_moe_few<1>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act, limit);
   return rc ? rc : cima_launch_result();
 }

@@ -7,6 +7,7 @@
 // float32 (sincosf, not the fast approximations); inv_freq[i] = theta^(-2i / rotary_dim) comes from
 // the host, computed in float64.  Pair (i, i + rotary_dim/2) of a head rotates:
 //   u_i' = u_i cos a - u_j sin a,   u_j' = u_i sin a + u_j cos a        (src/kernels.cu:397-414)
+// Sine and cosine are multiplied by `amp` (1 for a plain rotation; a rescaled table may ask for another amplitude).
 // Dimensions from rotary_dim on pass through.  Append: src/kernels.cu:440-454 (one sequence,
 // [kv_heads, max_seq, dim]); here the place comes from the slot's block table.
 #include "common.cuh"
@@ -15,7 +16,7 @@ template <typename TA>
 __global__ void __launch_bounds__(256)
 k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
               const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
-              const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int hd) {
+              const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int hd, float amp) {
   cima_pdl_wait();
   __shared__ float cs[128], sn[128];
   const int row = blockIdx.x;
@@ -24,8 +25,8 @@ k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, 
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float s, c;
     sincosf((float)pos * inv_freq[i], &s, &c);
-    cs[i] = c;
-    sn[i] = s;
+    cs[i] = c * amp;
+    sn[i] = s * amp;
   }
   __syncthreads();
   TA* base = qkv + (size_t)row * ld;
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(256)
 k_rope_append_bf16x8(__nv_bfloat16* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
                      const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
                      const int* __restrict__ seq_len, __nv_bfloat16* __restrict__ cache_in, CimaPaged pg, int nh, int nkv,
-                     int hd) {
+                     int hd, float amp) {
   cima_pdl_wait();
   __shared__ float cs[128], sn[128];
   const int row = blockIdx.x;
@@ -80,8 +81,8 @@ k_rope_append_bf16x8(__nv_bfloat16* __restrict__ qkv, int ld, const float* __res
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float s, c;
     sincosf((float)pos * inv_freq[i], &s, &c);
-    cs[i] = c;
-    sn[i] = s;
+    cs[i] = c * amp;
+    sn[i] = s * amp;
   }
   __syncthreads();
   __nv_bfloat16* base = qkv + (size_t)row * ld;
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(128)
 k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
                    const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
                    const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int nv, int hd,
-                   const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_dim, float eps) {
+                   const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_dim, float eps, float amp) {
   cima_pdl_wait();
   __shared__ __align__(16) float vals[4][256];
   __shared__ float rot_cos[128], rot_sin[128];
@@ -173,7 +174,12 @@ k_norm_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_f
   const int pos = row_pos[row];
   const int half = rotary_dim >> 1;
   if (blockIdx.x * 4 < nh + nkv) {                     // the row's angles once for the block's heads
-    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &rot_sin[i], &rot_cos[i]);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float sv, cv;
+      sincosf((float)pos * inv_freq[i], &sv, &cv);
+      rot_sin[i] = sv * amp;
+      rot_cos[i] = cv * amp;
+    }
     __syncthreads();
   }
   if (head >= nh + nkv + nv) return;
@@ -254,7 +260,7 @@ extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_f
                                 const int* row_pos, const int* row_seq, const int* seq_slot, const int* seq_len,
                                 void* cache, const int* table, int table_width, int ring, int page_size,
                                 int T, int nh, int nkv, int hd, int nv, const float* q_norm, const float* k_norm, int norm_dim,
-                                float eps, cudaStream_t stream) {
+                                float eps, float amp, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd > 256 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1))
     return cima_fail(CIMA_E_SIZE, "rope_append: head_dim %d (at most 256) and an even rotary_dim %d <= head_dim are needed", hd, rotary_dim);
@@ -271,23 +277,23 @@ extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_f
     const size_t bytes = dtype == CIMA_F32 ? 4 : 2;
     const bool vec = hd % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv % (4 * bytes)) == 0 && ((uintptr_t)cache % (4 * bytes)) == 0;
     if (vec) {
-      if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float, 4>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
-      else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16, 4>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+      if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float, 4>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps, amp);
+      else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16, 4>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps, amp);
       else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
       return rc_ ? rc_ : cima_launch_result();
     }
-    if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float, 1>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
-    else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16, 1>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps);
+    if (dtype == CIMA_F32) rc_ = cima_launch(k_norm_rope_append<float, 1>, grid, dim3(128), (size_t)0, stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps, amp);
+    else if (dtype == CIMA_BF16) rc_ = cima_launch(k_norm_rope_append<__nv_bfloat16, 1>, grid, dim3(128), (size_t)0, stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, nv, hd, q_norm, k_norm, norm_dim, eps, amp);
     else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
     return rc_ ? rc_ : cima_launch_result();
   }
   if (dtype == CIMA_F32)
-    { int rc_ = cima_launch(k_rope_append<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, hd); if (rc_) return rc_; }
+    { int rc_ = cima_launch(k_rope_append<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, hd, amp); if (rc_) return rc_; }
   else if (dtype == CIMA_BF16 && rotary_dim % 16 == 0 && hd % 8 == 0 && ld % 8 == 0 && rotary_dim <= 256 &&
            (((uintptr_t)qkv | (uintptr_t)cache) & 15) == 0)
-    { int rc_ = cima_launch(k_rope_append_bf16x8, dim3(T), dim3(256), (size_t)(0), stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd); if (rc_) return rc_; }
+    { int rc_ = cima_launch(k_rope_append_bf16x8, dim3(T), dim3(256), (size_t)(0), stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd, amp); if (rc_) return rc_; }
   else if (dtype == CIMA_BF16)
-    { int rc_ = cima_launch(k_rope_append<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd); if (rc_) return rc_; }
+    { int rc_ = cima_launch(k_rope_append<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd, amp); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
   return cima_launch_result();
 }

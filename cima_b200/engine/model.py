@@ -48,8 +48,16 @@ class Model:
                 raise ValueError(f"the schedule names layer {i}; the model has {len(spec.layers)}")
         self.blocks = [build_block(b, i, rt) for i, b in enumerate(spec.layers)]
         self.final_norm = build_norm(spec.final_norm, rt)
-        if spec.stream not in ("residual", "depth_average"):
-            raise ValueError(f"the model's stream '{spec.stream}' is neither 'residual' nor 'depth_average'")
+        if spec.stream not in ("residual", "depth_average", "hyper"):
+            raise ValueError(f"the model's stream '{spec.stream}' is none of 'residual', 'depth_average', 'hyper'")
+        if spec.stream == "hyper":
+            for i, b in enumerate(spec.layers):
+                if b.kind != "hyper" or b.streams != spec.streams:
+                    raise ValueError(f"a model of {spec.streams} streams needs blocks of kind 'hyper' with as many; layer {i} is "
+                                     f"'{b.kind}' with {b.streams}")
+            if spec.final_norm.kind != "rmsnorm":
+                raise ValueError("a model with several streams sums them in front of a final norm of kind 'rmsnorm'")
+            self._ones = None                               # the final reader's weights: the streams are summed
         self.depth = None                                   # what a layer reads: the stream itself, or a depth average
         if spec.stream == "depth_average":
             from ..parts.depth_average import DepthAverage
@@ -183,7 +191,8 @@ class Model:
         widest = max([int(getattr(b, "scratch_row", lambda: 0)()) for b in self.blocks] + [self.spec.hidden])
         return forecast(self.plan(), self._cache_requests(),
                         self.rt.dtype, max_tokens, self.spec.hidden, self.spec.vocab, widest, page_size, shares,
-                        extra_state, max_seqs or 0, streams=len(sched) + 2 if self.depth is not None else 1)
+                        extra_state, max_seqs or 0,
+                        streams=len(sched) + 2 if self.depth is not None else (self.spec.streams + 1 if self.spec.stream == "hyper" else 1))
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -288,6 +297,8 @@ class Model:
         K_, s = self.rt.kernels, self.spec
         if self.depth is not None:
             return self._forward_depth_average(batch)
+        if s.stream == "hyper":
+            return self._forward_hyper(batch)
         x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)
         # What a kernel leaves behind about the rows it wrote travels along as a RowsInfo, so that norms are
         # folded into the products around them (few rows) or run together with the residual add (many rows).
@@ -337,6 +348,49 @@ class Model:
                 nxt = self.final_norm if batch.want_all_in_order else None
             x, info = self.depth.after(stack, site, nxt, conv)
         return self.project(x, batch, info)
+
+    def _forward_hyper(self, batch: StepBatch) -> torch.Tensor:
+        """The same loop over several copies of the stream (``HyperBlock``): the embedding's rows become every copy and
+        the first block's input in one launch; each block's last launch forms the next block's input; behind the last
+        block the copies are summed and normed, for every row where all are wanted, else for the wanted rows only."""
+        K_, s = self.rt.kernels, self.spec
+        from ..parts.norm import RowsInfo
+        S, T = s.streams, batch.n_rows
+        order = [self.blocks[layer] for layer in s.schedule]
+        if self._ones is None:
+            self._ones = self.rt.vector(torch.ones(S))
+        last = (self._ones, self.final_norm)
+        e = self.rt.empty(T, s.hidden, dtype=torch.float32)
+        K_.embed(batch.tokens, self.embedding, e, s.embed_scale)
+        xs = self.rt.empty(T, S, s.hidden, dtype=torch.float32)
+        first = order[0].reader if order else (last if batch.want_all_in_order else None)
+        h = self.rt.empty(T, s.hidden) if first is not None else None
+        K_.hyper_connect(xs, e, None, None, 1.0, first[0] if first else None, first[1].weight if first else None,
+                         first[1].spec.eps if first else 0.0, h, spread=True)
+        info = RowsInfo(norm=first[1], h=h) if first is not None else None
+        for site, block in enumerate(order):
+            if site + 1 < len(order):
+                nxt = order[site + 1].reader
+            else:
+                nxt = last if batch.want_all_in_order else None
+            info = block.forward(xs, batch, self.cache, site, info, nxt)
+        if batch.n_want == 0:
+            return torch.empty((0, s.vocab), dtype=torch.float32, device=self.rt.device)
+        if info is not None and info.norm is self.final_norm and info.h is not None:
+            logits = self.head.logits(info.h)
+        else:
+            flat = xs.view(T, S * s.hidden)
+            if not batch.want_all_in_order:
+                picked = self.rt.empty(batch.n_want, S * s.hidden, dtype=torch.float32)
+                K_.gather_rows(flat, batch.want_rows, picked)
+                flat = picked
+            h = self.rt.empty(flat.shape[0], s.hidden)
+            K_.hyper_connect(flat.view(flat.shape[0], S, s.hidden), None, None, None, 1.0, last[0], self.final_norm.weight,
+                             self.final_norm.spec.eps, h)
+            logits = self.head.logits(h)
+        if s.logit_softcap > 0 and logits.shape[0] > 0:
+            K_.softcap(logits, s.logit_softcap)
+        return logits
 
     def project(self, x: torch.Tensor, batch: StepBatch, info=None) -> torch.Tensor:
         """Final norm and head at the wanted rows only; the logits capped softly where the spec says so."""

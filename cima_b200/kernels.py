@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 29
+ABI_VERSION = 30
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -39,6 +39,8 @@ ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "g
                # min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1): the kernels that take it take the limit L beside the code
                "swish_clamped": 4}
 GATED_ONLY = 4              # codes from here on are forms of the whole gated middle, not activations of the gate alone
+# activations of an ungated feed-forward's middle (``activate``): the gate activations and the square of ReLU
+UNGATED_ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu_new": 1, "gelu": 2, "relu": 3, "relu2": 5}
 
 
 class KernelError(RuntimeError):
@@ -68,14 +70,14 @@ _SIGNATURES = {
     "cima_linear_skinny_norm": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_qkv_rope_skinny": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                              _i, _i, _i, _i, _vp],
-    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp],
+    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _f, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                             _f, _i, _i, _i, _f, _i, _i, _vp],
-    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _f, _i, _i, _vp],
-    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
-    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp],
+                             _f, _i, _i, _i, _f, _i, _i, _vp, _vp],
+    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
+    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp, _vp],
+    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp, _vp],
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                 _f, _i, _vp, _i, _f, _vp],
+                                 _f, _i, _vp, _i, _f, _vp, _vp],
     "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_dyt": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "cima_dyt_add": [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -85,20 +87,26 @@ _SIGNATURES = {
     "cima_delta_prepare": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cima_group_rmsnorm_gate": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
     "cima_rms_mean": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _vp],
-    "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp],
+    "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "cima_moe_sort": [_vp, _i, _i, _vp, _vp, _vp, _vp],
-    "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cima_moe_sort_tiles": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "cima_moe_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
-    "cima_moe_few": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_gemm_tcgen05_pair_grouped": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+    "cima_moe_few": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "cima_gemm_tcgen05_pair_grouped": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp],
     "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
-    "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_latent_prepare": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _f, _i, _i, _vp, _f, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp,
+                            _vp, _i, _i, _i, _vp],
+    "cima_rope_rows": [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _f, _i, _vp, _i, _vp],
+    "cima_hyper_connect": [_vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _f, _vp, _i, _i, _i, _i, _vp],
+    "cima_activate": [_vp, _i, _sz, _i, _vp],
+    "cima_gate_rows": [_vp, _i, _i, _i, _vp, _i, _vp],
     "cima_head_linear_append": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp,
                                 _i, _vp],
-    "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _vp],
+    "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
     "cima_diff_combine": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
     "cima_scale_add_group_rmsnorm": [_vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _f, _vp],
@@ -408,11 +416,12 @@ class Kernels:
     # ------------------------------------------------------------------ attention
     def rope_append(self, qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, row_pos, row_seq, seq_slot,
                     seq_len, kv, n_heads: int, n_kv_heads: int, head_dim: int, v_heads: Optional[int] = None,
-                    qk_norm=None) -> None:
+                    qk_norm=None, amplitude: float = 1.0) -> None:
         """Rotate q and k of ``qkv`` in place and append k, v to the layer's pages (``kv`` a LayerKV or None).
         ``v_heads``: value heads of a row where they are fewer than the key heads (neighbouring key heads share one; the
         pages' value plane holds them in its first heads).  ``qk_norm = (wq, wk, dim, eps)``: before the rotation the first
-        ``dim`` values of every q (k) head are divided by their root mean square and multiplied by wq (wk) [dim]."""
+        ``dim`` values of every q (k) head are divided by their root mean square and multiplied by wq (wk) [dim].
+        ``amplitude``: a factor of every sine and cosine."""
         self._need(qkv, "qkv", None, 2); self._need(inv_freq, "inv_freq", torch.float32, 1)
         for n, t in (("row_pos", row_pos), ("row_seq", row_seq), ("seq_slot", seq_slot), ("seq_len", seq_len)):
             self._need(t, n, torch.int32, 1)
@@ -444,12 +453,13 @@ class Kernels:
             self._check(self.lib.cima_rope_append(qkv[r0:r1].data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], inv_freq.data_ptr(),
                                                   rotary_dim, row_pos[r0:r1].data_ptr(), row_seq[r0:r1].data_ptr(), seq_slot.data_ptr(),
                                                   seq_len.data_ptr(), *args, r1 - r0, n_heads, n_kv_heads, head_dim, nv, *norm,
-                                                  self._stream()), "rope_append")
+                                                  float(amplitude), self._stream()), "rope_append")
 
     def attention_plain(self, qkv: torch.Tensor, kv, row_pos, row_seq, seq_slot, seq_first_row, out: torch.Tensor,
                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int,
-                        from_cache: bool, sink: float = 0.0, keep_first: int = 0, v_group: int = 1) -> None:
+                        from_cache: bool, sink: float = 0.0, keep_first: int = 0, v_group: int = 1, head_sink=None) -> None:
         self._need(qkv, "qkv", None, 2); self._need(out, "out", qkv.dtype, 2)
+        self._need_head_sink(head_sink, n_heads)
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim):
             raise KernelError(f"attention: out is {tuple(out.shape)}, expected {(T, n_heads * head_dim)}")
@@ -466,7 +476,14 @@ class Kernels:
                                                   row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                                                   seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                   n_heads, n_kv_heads, head_dim, scale, window,
-                                                  1 if from_cache else 0, planes, sink, keep_first, v_group, self._stream()), "attention_plain")
+                                                  1 if from_cache else 0, planes, sink, keep_first, v_group, _ptr(head_sink),
+                                                  self._stream()), "attention_plain")
+
+    def _need_head_sink(self, head_sink, n_heads: int) -> None:
+        if head_sink is not None:
+            self._need(head_sink, "head_sink", torch.float32, 1)
+            if head_sink.numel() != n_heads:
+                raise KernelError(f"attention: head_sink has {head_sink.numel()} values, expected one for each of {n_heads} heads")
 
     def _attention_work(self, qkv, n_heads, n_kv_heads, head_dim, planes: int = 2):
         """(bytes, operations) of an attention launch while a step is profiled: the keys and values of the step's
@@ -498,65 +515,70 @@ class Kernels:
 
     def attention(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                   head_dim: int, scale: float, window: int, from_cache: bool, after_append: bool = False,
-                  sink: float = 0.0, keep_first: int = 0, v_group: int = 1) -> None:
+                  sink: float = 0.0, keep_first: int = 0, v_group: int = 1, head_sink=None) -> None:
         """Attention of a step's rows: over the step's own keys (a prompt from position 0) or over the
         cache.  Chooses the kernel; every choice computes the same function.  ``after_append``: the kernel
         launched just before wrote nothing but ``qkv`` and the newest position of each sequence in the cache.
         ``sink``: that many entries of score 0 that carry no value join every row's denominator (0: an ordinary softmax).
         ``keep_first``: with a window, the first so many positions of a sequence stay visible below it.  ``v_group``: that
         many neighbouring key heads share one value head (a step's rows and the pages' value plane hold
-        n_kv_heads / v_group value heads)."""
+        n_kv_heads / v_group value heads).  ``head_sink`` (float32 [n_heads], instead of ``sink``): head h's denominator
+        also holds exp(head_sink[h]), an entry that is not scaled and carries no value."""
         general = keep_first > 0 or v_group > 1        # the tcgen05 kernels take neither
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and batch.n_rows == batch.n_seqs):
             return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
                                          scale, window, batch.max_len, early=after_append, sink=sink,
-                                         keep_first=keep_first, v_group=v_group)
+                                         keep_first=keep_first, v_group=v_group, head_sink=head_sink)
         many = (not general and qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
                 and getattr(batch, "n_q_tiles_tc", 0) > 0 and getattr(batch, "max_rows", 0) >= TC_ATTENTION_MIN_LEN)
         if from_cache and many and kv.page_size == 64 and kv.storage.numel() // head_dim < 2 ** 31:
-            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, kv=kv, sink=sink)
+            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, kv=kv, sink=sink,
+                                             head_sink=head_sink)
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink,
-                                         keep_first=keep_first, v_group=v_group)
+                                         keep_first=keep_first, v_group=v_group, head_sink=head_sink)
         if not from_cache and many:
-            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
+            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink,
+                                             head_sink=head_sink)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_prefill(qkv, batch.q_tile_seq, batch.q_tile_row0, batch.seq_first_row, out,
                                           n_heads, n_kv_heads, head_dim, scale, window, sink=sink,
-                                          keep_first=keep_first, v_group=v_group)
+                                          keep_first=keep_first, v_group=v_group, head_sink=head_sink)
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
                              n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink=sink, keep_first=keep_first,
-                             v_group=v_group)
+                             v_group=v_group, head_sink=head_sink)
 
     def attention_prefill(self, qkv: torch.Tensor, tile_seq, tile_row0, seq_first_row, out: torch.Tensor,
                           n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, sink: float = 0.0,
-                          keep_first: int = 0, v_group: int = 1) -> None:
+                          keep_first: int = 0, v_group: int = 1, head_sink=None) -> None:
         """Flash attention of ragged prompts that start at position 0 (bf16, head_dim <= 128);
         ``tile_seq``/``tile_row0`` list the blocks of 64 query rows."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         for n, t in (("tile_seq", tile_seq), ("tile_row0", tile_row0), ("seq_first_row", seq_first_row)):
             self._need(t, n, torch.int32, 1)
         T = qkv.shape[0]
+        self._need_head_sink(head_sink, n_heads)
         if tuple(out.shape) != (T, n_heads * head_dim) or tile_seq.numel() != tile_row0.numel():
             raise KernelError(f"attention_prefill: out {tuple(out.shape)} or the block list do not fit")
         if not self._admit("attention_prefill", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         self._check(self.lib.cima_attention_prefill(qkv.data_ptr(), qkv.shape[1], tile_seq.data_ptr(), tile_row0.data_ptr(),
                                                     seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                     tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, sink,
-                                                    keep_first, v_group, self._stream()), "attention_prefill")
+                                                    keep_first, v_group, _ptr(head_sink), self._stream()), "attention_prefill")
 
     def attention_extend(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                          head_dim: int, scale: float, window: int, sink: float = 0.0, keep_first: int = 0,
-                         v_group: int = 1) -> None:
+                         v_group: int = 1, head_sink=None) -> None:
         """Flash attention of sequences that bring several rows to a cache that already holds keys (bf16, pages of
         64, head_dim <= 128): the rows of sequence s stand at positions seq_len[s] - rows .. seq_len[s] - 1, and all
         keys, the step's own included, are read from the layer's pages.  ``batch`` brings the blocks of 64 rows."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
         T = qkv.shape[0]
+        self._need_head_sink(head_sink, n_heads)
         if tuple(out.shape) != (T, n_heads * head_dim) or batch.q_tile_seq.numel() != batch.q_tile_row0.numel():
             raise KernelError(f"attention_extend: out {tuple(out.shape)} or the block list do not fit")
         if not self._admit("attention_extend", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim, kv.planes)): return
@@ -565,10 +587,10 @@ class Kernels:
             batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(), out.data_ptr(), out.shape[1],
             T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, kv.planes, sink, keep_first, v_group,
-            self._stream()), "attention_extend")
+            _ptr(head_sink), self._stream()), "attention_extend")
 
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                             head_dim: int, scale: float, window: int, kv=None, sink: float = 0.0) -> None:
+                             head_dim: int, scale: float, window: int, kv=None, sink: float = 0.0, head_sink=None) -> None:
         """Flash attention of ragged prompts on the tcgen05 tensor cores (bf16, head_dim 64 or 128): blocks of 128
         query rows, both products with their results in tensor memory.  ``batch`` brings the blocks
         (``q_tile_tc_*``).  Without ``kv`` the sequences start at position 0 and the keys are the step's own rows;
@@ -576,6 +598,7 @@ class Kernels:
         seq_len[s] - rows .. seq_len[s] - 1 and all keys come from the pages."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         T = qkv.shape[0]
+        self._need_head_sink(head_sink, n_heads)
         if tuple(out.shape) != (T, n_heads * head_dim) or batch.n_q_tiles_tc <= 0:
             raise KernelError(f"attention_prefill_tc: out {tuple(out.shape)} or the block list do not fit")
         if self._error_flag is None:
@@ -588,18 +611,18 @@ class Kernels:
                 batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.storage.shape[0], kv.block_table.data_ptr(),
                 kv.block_table.shape[1], kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(),
                 out.data_ptr(), out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
-                self._error_flag.data_ptr(), kv.planes, sink, self._stream()), "attention_extend_tc")
+                self._error_flag.data_ptr(), kv.planes, sink, _ptr(head_sink), self._stream()), "attention_extend_tc")
             return
         self._check(self.lib.cima_attention_prefill_tc(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_tc_seq.data_ptr(), batch.q_tile_tc_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), out.data_ptr(),
             out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
-            self._error_flag.data_ptr(), sink, self._stream()), "attention_prefill_tc")
+            self._error_flag.data_ptr(), sink, _ptr(head_sink), self._stream()), "attention_prefill_tc")
 
     def attention_decode(self, qkv: torch.Tensor, kv, seq_slot, seq_len, out: torch.Tensor, n_heads: int,
                          n_kv_heads: int, head_dim: int, scale: float, window: int, max_len: int = 0,
                          n_splits: Optional[int] = None, early: bool = False, sink: float = 0.0, keep_first: int = 0,
-                         v_group: int = 1) -> None:
+                         v_group: int = 1, head_sink=None) -> None:
         """One query per sequence over the paged cache (bf16, pages of 64, head_dim <= 128), keys split
         over ``n_splits`` blocks per (sequence, kv head).  ``max_len`` (0 = unknown) only bounds the
         number of splits chosen here.  ``early``: the kernel launched just before this one wrote neither
@@ -608,6 +631,7 @@ class Kernels:
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
         B = qkv.shape[0]
+        self._need_head_sink(head_sink, n_heads)
         if tuple(out.shape) != (B, n_heads * head_dim) or seq_slot.numel() < B or seq_len.numel() < B:
             raise KernelError(f"attention_decode: out {tuple(out.shape)} / sequences do not fit {B} rows")
         if n_splits is None:
@@ -639,7 +663,7 @@ class Kernels:
             qkv.data_ptr(), qkv.shape[1], kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, seq_slot.data_ptr(), seq_len.data_ptr(), _ptr(part_o), _ptr(part_ml),
             out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, int(early),
-            kv.planes, sink, keep_first, v_group, self._stream()), "attention_decode")
+            kv.planes, sink, keep_first, v_group, _ptr(head_sink), self._stream()), "attention_decode")
         if n_splits > 1:
             self.launches += 1
 
@@ -729,11 +753,16 @@ class Kernels:
 
     FUSED_APPEND_ROWS = 8       # a step of at most this many rows appends its latents in the launch of its first head product
 
-    def head_linear(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, append=None) -> None:
+    def head_linear(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, append=None, a_head: Optional[int] = None,
+                    out_head: Optional[int] = None) -> None:
         """out[t, h, :] = a[t, h, :] @ w[h].T for every head: a [T, heads * K] (rows may be slices of a wider
         matrix), w [heads, N, K], out [T, heads * N]; one dtype.  ``append = (raw, g, eps, kv, batch)``: the arguments
         of ``latent_append`` for the same rows, done by the same launch (a decode step's few rows) or, for more rows,
-        by a launch of its own first."""
+        by a launch of its own first.  ``a_head`` / ``out_head``: values from one head's start to the next in a row of
+        ``a`` / ``out`` where a head there is wider than K / N (the product reads a head's first K values and writes its
+        first N; what lies behind them is left alone)."""
+        if a_head is not None or out_head is not None:
+            return self._head_linear_strided(a, w, out, int(a_head or w.shape[2]), int(out_head or w.shape[1]))
         if append is not None and (a.shape[0] > self.FUSED_APPEND_ROWS or a.shape[0] * (w.shape[2] + 3) * 4 > 48 * 1024):
             self.latent_append(*append)
             append = None
@@ -763,7 +792,135 @@ class Kernels:
                 batch.seq_slot.data_ptr(), R, self._stream()), "head_linear_append")
             return
         self._check(self.lib.cima_head_linear(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K,
-                                              a.stride(0), out.stride(0), self._stream()), "head_linear")
+                                              a.stride(0), out.stride(0), K, N, self._stream()), "head_linear")
+
+    def _head_linear_strided(self, a, w, out, a_head: int, out_head: int) -> None:
+        self._need(w, "w", a.dtype, 3)
+        heads, N, K = w.shape
+        T = a.shape[0]
+        if (a.dim() != 2 or out.dim() != 2 or a.stride(1) != 1 or out.stride(1) != 1 or out.dtype is not a.dtype or out.shape[0] != T
+                or a_head < K or out_head < N or a.shape[1] < (heads - 1) * a_head + K or out.shape[1] < (heads - 1) * out_head + N):
+            raise KernelError(f"head_linear: a {tuple(a.shape)} in heads of {a_head}, w {tuple(w.shape)}, out {tuple(out.shape)} in heads "
+                              f"of {out_head} do not agree")
+        if not self._admit("head_linear", (w.numel() + T * heads * (K + N)) * a.element_size(), 2.0 * T * heads * N * K): return
+        if a.dtype is torch.bfloat16 and T > 8:
+            # many bfloat16 rows: the library's batched product over the heads' columns
+            self.library_launches += 1
+            av = torch.as_strided(a, (heads, T, K), (a_head, a.stride(0), 1))
+            ov = torch.as_strided(out, (heads, T, N), (out_head, out.stride(0), 1))
+            ov.copy_(torch.bmm(av, w.transpose(1, 2)))
+            return
+        self._check(self.lib.cima_head_linear(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K,
+                                              a.stride(0), out.stride(0), a_head, out_head, self._stream()), "head_linear")
+
+    def latent_prepare(self, ql: torch.Tensor, first: int, q_norm, cq, c_norm: torch.Tensor, eps: float, rank: int, rot: int,
+                       inv_freq, amplitude: float, interleaved: bool, kv, batch, step_rows=None) -> None:
+        """What stands between a latent attention's first product and its attention, for every row of ``ql`` =
+        [``first`` values | ``rank`` | ``rot``]: with ``cq`` [T, first] the first part is a query latent, cq = rms(part) * q_norm;
+        c = rms(second part) * c_norm; the third part is rotated at the row's position (pairs of neighbours where
+        ``interleaved``, else (i, i + rot / 2); sine and cosine times ``amplitude``); [c | rotated part] goes to the row's
+        place in the layer's one-plane pages (unless a later row of the step takes that place of a ring) and, with
+        ``step_rows`` = (buffer [T, ld], column), to columns column .. column + rank + rot and once more behind them (a
+        prompt's attention reads its keys and its values there).  Sums of squares, norms and angles are float32."""
+        self._need(ql, "ql", None, 2); self._need(c_norm, "c_norm", torch.float32, 1)
+        T, ld = ql.shape
+        kd = rank + rot
+        q_rank = 0
+        if cq is not None:
+            self._need(cq, "cq", ql.dtype, 2); self._need(q_norm, "q_norm", torch.float32, 1)
+            q_rank = first
+            if tuple(cq.shape) != (T, first) or q_norm.numel() != first:
+                raise KernelError(f"latent_prepare: cq {tuple(cq.shape)} / q_norm {tuple(q_norm.shape)} do not fit a query latent of {first}")
+        if ld < first + kd or c_norm.numel() != rank or rot % 2:
+            raise KernelError(f"latent_prepare: rows of {ld} values do not hold {first} + {rank} + {rot}, or the norm's weight does not fit")
+        if rot:
+            self._need(inv_freq, "inv_freq", torch.float32, 1)
+            if inv_freq.numel() != rot // 2:
+                raise KernelError(f"latent_prepare: inv_freq has {inv_freq.numel()} entries, expected {rot // 2}")
+        self._need(kv.storage, "cache", ql.dtype, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
+        if tuple(kv.storage.shape[1:]) != (1, 1, kv.page_size, kd):
+            raise KernelError(f"latent_prepare: cache pages are {tuple(kv.storage.shape)}, expected [*, 1, 1, {kv.page_size}, {kd}]")
+        sr, sr_ld, sr_col = (None, 0, 0)
+        if step_rows is not None:
+            buf, sr_col = step_rows
+            self._need(buf, "step_rows", ql.dtype, 2)
+            if buf.shape[0] != T or buf.shape[1] < sr_col + 2 * kd:
+                raise KernelError(f"latent_prepare: step rows {tuple(buf.shape)} do not hold two copies of {kd} values from column {sr_col} on")
+            sr, sr_ld = buf.data_ptr(), buf.stride(0)
+        if not self._admit("latent_prepare", T * (ld + q_rank + (3 if sr else 1) * kd) * ql.element_size()): return
+        self._check(self.lib.cima_latent_prepare(
+            ql.data_ptr(), dtype_code(ql.dtype), ld, first, _ptr(q_norm) if cq is not None else None, _ptr(cq), q_rank,
+            c_norm.data_ptr(), eps, rank, rot, _ptr(inv_freq) if rot else None, float(amplitude), int(bool(interleaved)),
+            kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size,
+            batch.row_pos.data_ptr(), batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(),
+            sr, sr_ld, sr_col, T, self._stream()), "latent_prepare")
+
+    def rope_rows(self, q: torch.Tensor, q_off: int, q_head: int, out: torch.Tensor, o_off: int, o_head: int, heads: int, rot: int,
+                  inv_freq: torch.Tensor, amplitude: float, interleaved: bool, row_pos: torch.Tensor) -> None:
+        """out[t, h * o_head + o_off + j] = the j-th of the ``rot`` values q[t, h * q_head + q_off ...] rotated at row t's
+        position, for every head (pairs as in ``latent_prepare``); float32 angles, one rounding at the store."""
+        self._need(q, "q", None, 2); self._need(out, "out", q.dtype, 2); self._need(inv_freq, "inv_freq", torch.float32, 1)
+        self._need(row_pos, "row_pos", torch.int32, 1)
+        T = q.shape[0]
+        if (out.shape[0] != T or rot % 2 or inv_freq.numel() != rot // 2 or q.shape[1] < (heads - 1) * q_head + q_off + rot
+                or out.shape[1] < (heads - 1) * o_head + o_off + rot or row_pos.numel() < T):
+            raise KernelError(f"rope_rows: q {tuple(q.shape)}, out {tuple(out.shape)}, {heads} heads of {rot} rotating values do not agree")
+        if not self._admit("rope_rows", 2 * T * heads * rot * q.element_size()): return
+        self._check(self.lib.cima_rope_rows(q.data_ptr(), dtype_code(q.dtype), q.stride(0), q_off, q_head, out.data_ptr(), out.stride(0),
+                                            o_off, o_head, heads, rot, inv_freq.data_ptr(), float(amplitude), int(bool(interleaved)),
+                                            row_pos.data_ptr(), T, self._stream()), "rope_rows")
+
+    # ------------------------------------------------------------------ several copies of the stream, ungated activation
+    def hyper_connect(self, xs: torch.Tensor, y, C, b, mult: float, a_next, w_next, eps: float, h, spread: bool = False) -> None:
+        """The streams xs [T, S, W] (float32, in place) take a sublayer's output and are read for the next one:
+            with y [T, W] float32:   X_t <- sum_s C[s, t] X_s + mult * b[t] * y   for all t from the old X
+            (``spread``: X_t <- y for all t; C and b are not read)
+            with a_next [S]:         u = sum_s a_next[s] X_s (the new X);  h = u / sqrt(mean(u^2) + eps) * w_next
+        ``h`` [T, W] in float32 or bfloat16.  Either half may be absent.  Everything is float32; one rounding at the
+        store of h."""
+        self._need(xs, "xs", torch.float32, 3)
+        T, S, W = xs.shape
+        if y is not None:
+            self._need(y, "y", torch.float32, 2)
+            if tuple(y.shape) != (T, W):
+                raise KernelError(f"hyper_connect: y is {tuple(y.shape)}, expected {(T, W)}")
+            if not spread:
+                self._need(C, "C", torch.float32); self._need(b, "b", torch.float32)
+                if C.numel() != S * S or b.numel() != S:
+                    raise KernelError(f"hyper_connect: C has {C.numel()} and b {b.numel()} values for {S} streams")
+        if a_next is not None:
+            self._need(a_next, "a_next", torch.float32); self._need(w_next, "w_next", torch.float32, 1); self._need(h, "h", None, 2)
+            if a_next.numel() != S or w_next.numel() != W or tuple(h.shape) != (T, W):
+                raise KernelError(f"hyper_connect: a_next {tuple(a_next.shape)}, w_next {tuple(w_next.shape)}, h {tuple(h.shape)} do not fit {(T, S, W)}")
+        if T == 0:
+            return
+        nbytes = T * W * ((2 * S if y is not None and not spread else S) * 4 + (4 if y is not None else 0)
+                          + (h.element_size() if a_next is not None else 0))
+        if not self._admit("hyper_connect", nbytes): return
+        self._check(self.lib.cima_hyper_connect(xs.data_ptr(), _ptr(y), _ptr(C) if not spread else None, _ptr(b) if not spread else None,
+                                                float(mult), int(bool(spread)), _ptr(a_next), _ptr(w_next) if a_next is not None else None,
+                                                float(eps), _ptr(h) if a_next is not None else None,
+                                                dtype_code(h.dtype) if a_next is not None else F32, T, S, W, self._stream()), "hyper_connect")
+
+    def activate(self, z: torch.Tensor, act: int) -> None:
+        """z <- act(z) in place, ``act`` one of ``UNGATED_ACTIVATIONS``' codes; float32 inside, one rounding at the store."""
+        self._need(z, "z")
+        if z.numel() == 0:
+            return
+        if not self._admit("activate", 2 * z.numel() * z.element_size()): return
+        self._check(self.lib.cima_activate(z.data_ptr(), dtype_code(z.dtype), z.numel(), int(act), self._stream()), "activate")
+
+    def gate_rows(self, z: torch.Tensor, g: torch.Tensor, col: int) -> None:
+        """z[t, :] *= sigmoid(g[t, col]) in place: g float32 [T, n]."""
+        self._need(z, "z", None, 2); self._need(g, "g", torch.float32, 2)
+        T, N = z.shape
+        if g.shape[0] != T or not (0 <= col < g.shape[1]):
+            raise KernelError(f"gate_rows: g {tuple(g.shape)} has no column {col} for the {T} rows of z")
+        if T == 0:
+            return
+        if not self._admit("gate_rows", 2 * z.numel() * z.element_size()): return
+        self._check(self.lib.cima_gate_rows(z.data_ptr(), dtype_code(z.dtype), T, N, g[:, col:].data_ptr(), g.stride(0), self._stream()),
+                    "gate_rows")
 
     # ------------------------------------------------------------------ Dynamic Tanh, bigram embedding
     def dyt(self, x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
@@ -996,14 +1153,24 @@ class Kernels:
     ROUTE_SORT_ROWS = 64        # a step of at most this many rows orders its pairs by expert in the routing launch
 
     def moe_route(self, scores: torch.Tensor, top: int, groups: int, keep: int, scale: float, idx: torch.Tensor,
-                  wgt: torch.Tensor, order: bool = False):
+                  wgt: torch.Tensor, order: bool = False, experts: Optional[int] = None, softmax: bool = False, correction=None):
         """``scores`` float32 [T, E] holds the router's logits (it is scratch afterwards).  s = sigmoid(logits); the
         experts form ``groups`` equal groups of neighbours, a group's score is the sum of its two best, the best
         ``keep`` groups stay, and the ``top`` best experts among them are chosen: idx [T, top] int32, and their weights
         s / (sum of the chosen s + 1e-20) * scale in wgt [T, top] float32.  ``order`` (at most ``ROUTE_SORT_ROWS`` rows): the
-        same launch also orders the pairs by expert; what it returns goes to ``moe_experts`` as ``ordered``."""
+        same launch also orders the pairs by expert; what it returns goes to ``moe_experts`` as ``ordered``.
+        ``experts``: the first so many columns of ``scores`` are the experts' (default: all; further columns are left alone).
+        ``softmax``: s = softmax(logits) over the experts instead of the sigmoid.  ``correction`` (float32 [experts]): added to s
+        where groups and experts are compared; the weights are made of s itself."""
         self._need(scores, "scores", torch.float32, 2); self._need(idx, "idx", torch.int32, 2); self._need(wgt, "wgt", torch.float32, 2)
-        T, E = scores.shape
+        T, ld = scores.shape
+        E = ld if experts is None else int(experts)
+        if not (0 < E <= ld):
+            raise KernelError(f"moe_route: {E} experts in rows of {ld} scores")
+        if correction is not None:
+            self._need(correction, "correction", torch.float32, 1)
+            if correction.numel() != E:
+                raise KernelError(f"moe_route: the correction has {correction.numel()} values for {E} experts")
         if tuple(idx.shape) != (T, top) or tuple(wgt.shape) != (T, top):
             raise KernelError(f"moe_route: idx {tuple(idx.shape)} / wgt {tuple(wgt.shape)} are not {(T, top)}")
         meta = None
@@ -1011,12 +1178,13 @@ class Kernels:
             meta = torch.empty(2 * (E + 1) + T * top, dtype=torch.int32, device=scores.device)
         if not self._admit("moe_route", T * (E * 8 + top * 8)): return meta
         parts = (meta[:E + 1].data_ptr(), meta[E + 1:2 * (E + 1)].data_ptr(), meta[2 * (E + 1):].data_ptr()) if meta is not None else (None, None, None)
-        self._check(self.lib.cima_moe_route(scores.data_ptr(), T, E, top, groups, keep, scale, idx.data_ptr(), wgt.data_ptr(),
-                                            *parts, self._stream()), "moe_route")
+        self._check(self.lib.cima_moe_route(scores.data_ptr(), T, E, ld, top, groups, keep, scale, int(bool(softmax)), _ptr(correction),
+                                            idx.data_ptr(), wgt.data_ptr(), *parts, self._stream()), "moe_route")
         return meta
 
     def moe_experts(self, h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
-                    x: torch.Tensor, act: int = 0, assign: bool = False, ordered: Optional[torch.Tensor] = None) -> None:
+                    x: torch.Tensor, act: int = 0, assign: bool = False, ordered: Optional[torch.Tensor] = None,
+                    limit: float = 0.0) -> None:
         """x[t] += (with ``assign``: =) sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
         gate_up [E, 2 ff, H] (an expert's gate rows, then its up rows), down [E, H, ff]; x float32 [T, H].  Four launches:
         the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum.  The
@@ -1035,7 +1203,7 @@ class Kernels:
         dev = h.device
         bf16 = h.dtype is torch.bfloat16 and gate_up.dtype is torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and h.stride(0) % 8 == 0
         if bf16 and P >= self.MOE_TC_PAIRS:
-            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act, assign)
+            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act, assign, limit)
         few = bf16 and P <= self.MOE_FEW_PAIRS
         meta = ordered if ordered is not None else torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
         offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
@@ -1050,26 +1218,26 @@ class Kernels:
         if self._admit(f"{name}[gate|up]", touched * 2 * ff * H * wb + P * (H + ff) * h.element_size(), 4.0 * P * ff * H):
             if few:
                 self._check(self.lib.cima_moe_few(h.data_ptr(), h.stride(0), gate_up.data_ptr(), z.data_ptr(), offsets.data_ptr(),
-                                                  tiles.data_ptr(), perm.data_ptr(), P, E, top, ff, H, 0, act, self._stream()), "moe_few")
+                                                  tiles.data_ptr(), perm.data_ptr(), P, E, top, ff, H, 0, act, limit, self._stream()), "moe_few")
             else:
                 self._check(self.lib.cima_moe_gemm(h.data_ptr(), dtype_code(h.dtype), h.stride(0), gate_up.data_ptr(),
                                                    dtype_code(gate_up.dtype), z.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
-                                                   perm.data_ptr(), P, E, top, ff, H, 0, act, self._stream()), "moe_gemm")
+                                                   perm.data_ptr(), P, E, top, ff, H, 0, act, limit, self._stream()), "moe_gemm")
         if self._admit(f"{name}[down]", touched * ff * H * wb + P * (ff * h.element_size() + H * 4), 2.0 * P * ff * H):
             if few:
                 self._check(self.lib.cima_moe_few(z.data_ptr(), ff, down.data_ptr(), y.data_ptr(), offsets.data_ptr(),
-                                                  tiles.data_ptr(), perm.data_ptr(), P, E, top, H, ff, 1, 0, self._stream()), "moe_few")
+                                                  tiles.data_ptr(), perm.data_ptr(), P, E, top, H, ff, 1, 0, 0.0, self._stream()), "moe_few")
             else:
                 self._check(self.lib.cima_moe_gemm(z.data_ptr(), dtype_code(z.dtype), ff, down.data_ptr(), dtype_code(down.dtype),
                                                    y.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(), P, E, top,
-                                                   H, ff, 1, 0, self._stream()), "moe_gemm")
+                                                   H, ff, 1, 0, 0.0, self._stream()), "moe_gemm")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
             self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), None, x.data_ptr(), T, top, H, int(assign), self._stream()), "moe_combine")
 
     MOE_TC_PAIRS = 1024      # from this many (row, choice) pairs on, bfloat16 experts run on the tcgen05 tiles of 256 pairs
     MOE_FEW_PAIRS = 128      # up to this many, a warp computes a feature for the pairs of an expert (a decode step)
 
-    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act, assign=False) -> None:
+    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act, assign=False, limit: float = 0.0) -> None:
         """Many pairs in bfloat16: every expert's pairs are laid out from a multiple of 256 rows on (the rows of h copied
         there), so that each tile of the tcgen05 product multiplies with one expert's matrix."""
         T, H = h.shape
@@ -1093,11 +1261,11 @@ class Kernels:
                         "moe_gather_rows")
         if self._admit("gemm_tcgen05_pair_grouped[gate|up]", E * 2 * ff * H * 2 + P * (H + ff) * 2, 4.0 * P * ff * H):
             self._check(self.lib.cima_gemm_tcgen05_pair_grouped(hs.data_ptr(), gate_up.data_ptr(), z.data_ptr(), SK_SWIGLU,
-                                                                n_tiles * TILE, 2 * ff, E, H, ff, ff, act, tile_expert.data_ptr(),
+                                                                n_tiles * TILE, 2 * ff, E, H, ff, ff, act, limit, tile_expert.data_ptr(),
                                                                 flag.data_ptr(), self._stream()), "gemm_tcgen05_pair_grouped")
         if self._admit("gemm_tcgen05_pair_grouped[down]", E * ff * H * 2 + P * (ff * 2 + H * 4), 2.0 * P * ff * H):
             self._check(self.lib.cima_gemm_tcgen05_pair_grouped(z.data_ptr(), down.data_ptr(), y.data_ptr(), SK_STORE_F32,
-                                                                n_tiles * TILE, H, E, ff, H, 0, 0, tile_expert.data_ptr(),
+                                                                n_tiles * TILE, H, E, ff, H, 0, 0, 0.0, tile_expert.data_ptr(),
                                                                 flag.data_ptr(), self._stream()), "gemm_tcgen05_pair_grouped")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
             self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), pos.data_ptr(), x.data_ptr(), T, top, H,

@@ -8,7 +8,11 @@ h / (heads / kv_heads), no output bias unless the spec says so.
 
 Every size (heads, kv heads, head_dim, window, scale, bias flags) is a field of the spec.  Two more are ``params``:
 ``v_dim``, a value size that differs from the key size, and ``sink``, a number of entries of score 0 that carry no
-value and join every row's softmax denominator (1: p_j = exp(s_j) / (1 + sum exp(s))).  Keys and values live in the
+value and join every row's softmax denominator (1: p_j = exp(s_j) / (1 + sum exp(s))); ``keep_first``: with a window, a
+sequence's first so many positions stay visible below it, at their own positions (such a layer keeps every page: a ring
+would hand the first pages on).  A position encoding whose pairs are neighbours (``interleaved``) is served by
+permuting the rows of W_q and W_k at load, alike in every head, which leaves every score as it is; a position
+encoding's ``amplitude`` multiplies sine and cosine in the rotating kernel.  Keys and values live in the
 cache at one size, the larger of the two rounded up to 16: the rows of W_q, W_k, W_v (and the columns of W_o) that
 pad a head are zero, so scores and outputs are what the unpadded sizes give.
 """
@@ -28,6 +32,7 @@ class Attention:
     def __init__(self, spec, layer: int, rt):
         self.dim, self.vdim = spec.head_dim, int(spec.params.get("v_dim", spec.head_dim))
         self.sink = float(spec.params.get("sink", 0.0))
+        self.keep_first = int(spec.params.get("keep_first", 0)) if spec.window else 0
         self.padded = self.dim != self.vdim or self.dim % 16 != 0
         self.hd = -(-max(self.dim, self.vdim) // 16) * 16 if self.padded else self.dim      # a head's size in a step's rows and in the cache
         if min(self.dim, self.vdim) <= 0 or self.hd > 256:
@@ -73,7 +78,16 @@ class Attention:
         if s.qkv_bias:
             bias = torch.cat([tensors[f"{prefix}{names[k]}.bias"].float() for k in ("q", "k", "v")])
         sizes = {"q": (s.n_heads, self.dim), "k": (s.n_kv_heads, self.dim), "v": (s.n_kv_heads, self.vdim)}
-        self.qkv = Linear([self._pad_rows(tensors[f"{prefix}{names[k]}{sfx}"], *sizes[k]) for k in ("q", "k", "v")], bias, self.rt)
+
+        def rows(k):
+            t = tensors[f"{prefix}{names[k]}{sfx}"]
+            if k != "v" and self.position.interleaved:
+                t = t[self.position.to_half_split(sizes[k][0], self.dim).to(t.device)]
+            return self._pad_rows(t, *sizes[k])
+
+        if self.position.interleaved and s.qkv_bias:
+            raise ValueError("attention: neighbouring rotary pairs with biases on q and k are not implemented")
+        self.qkv = Linear([rows(k) for k in ("q", "k", "v")], bias, self.rt)
         ob = tensors[f"{prefix}{names['o']}.bias"] if s.out_bias else None
         wo = tensors[f"{prefix}{names['o']}{sfx}"]
         if self.vdim != self.hd:
@@ -91,7 +105,13 @@ class Attention:
         for key, rows, heads, size in (("q", self.qd, s.n_heads, self.dim), ("k", self.kvd, s.n_kv_heads, self.dim),
                                        ("v", self.kvd, s.n_kv_heads, self.vdim)):
             w = self.qkv.weight[r:r + rows]
-            out[f"{prefix}{names[key]}{sfx}"] = w if size == self.hd else w.view(heads, self.hd, -1)[:, :size].reshape(heads * size, -1)
+            w = w if size == self.hd else w.view(heads, self.hd, -1)[:, :size].reshape(heads * size, -1)
+            if key != "v" and self.position.interleaved:
+                order = self.position.to_half_split(heads, size).to(w.device)
+                back = torch.empty_like(w)
+                back[order] = w
+                w = back
+            out[f"{prefix}{names[key]}{sfx}"] = w
             if self.qkv.bias is not None:
                 out[f"{prefix}{names[key]}.bias"] = self.qkv.bias[r:r + rows]
             r += rows
@@ -118,7 +138,7 @@ class Attention:
     def cache_requests(self, site: int) -> List[object]:
         if self.spec.cache_from is not None:
             return []
-        return [KVRequest(self.spec.n_kv_heads, self.hd, self.spec.window)]
+        return [KVRequest(self.spec.n_kv_heads, self.hd, 0 if self.keep_first > 0 else self.spec.window)]
 
     # ------------------------------------------------------------------ step
     takes_pending_norm = True      # h may be a NormedInput: the q/k/v product folds the norm in when it can
@@ -137,7 +157,7 @@ class Attention:
         writes = s.cache_from is None
         rows = h.shape[0]
         if (not batch.prefill and writes and self.qkv._skinny(rows) and kv.storage.dtype is torch.bfloat16
-                and self.position.rotary_dim == self.hd and hasattr(K_, "qkv_rope")):
+                and self.position.rotary_dim == self.hd and self.position.amplitude == 1.0 and hasattr(K_, "qkv_rope")):
             # decoding: projection, rotation and the append to the cache as one kernel
             qkv = self.rt.empty(rows, self.qd + 2 * self.kvd)
             if self.qkv._folds(h, rows):
@@ -150,16 +170,22 @@ class Attention:
                             s.n_kv_heads, self.hd)
         else:
             qkv = self.qkv.store(h)
-            K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
-                           batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, self.hd)
+            if self.position.amplitude != 1.0:
+                K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
+                               batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, self.hd,
+                               amplitude=self.position.amplitude)
+            else:
+                K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
+                               batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, self.hd)
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
+        more = {}
         if self.sink:
-            K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, self.hd, s.scale, s.window, from_cache,
-                         after_append=True, sink=self.sink)
-        else:
-            K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, self.hd, s.scale, s.window, from_cache,
-                         after_append=True)
+            more["sink"] = self.sink
+        if self.keep_first:
+            more["keep_first"] = self.keep_first
+        K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, self.hd, s.scale, s.window, from_cache,
+                     after_append=True, **more)
         return att
 
 

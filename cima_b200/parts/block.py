@@ -4,7 +4,8 @@ feeds both sublayers, the mixer optionally through a short causal convolution, t
 ``sandwich``: a norm in front of and behind each sublayer, x += m * post(mixer(norm(x))); x += m * post(ffn(norm(x))) with
 the spec's ``residual_mult`` m; the feed-forward with its two norms may be absent.  ``postnorm``: the norm stands behind
 the sum, x = norm(a x + mixer(x)); x = norm(a x + feed_forward(x)) with the spec's ``stream_mult`` a; the sublayers read the
-stream itself and the feed-forward may be absent.  The block builds its parts from the spec through the
+stream itself and the feed-forward may be absent.  ``hyper``: the model carries several copies of the stream, and a
+sublayer reads a weighted sum of them and writes into all of them (``HyperBlock``).  The block builds its parts from the spec through the
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
@@ -368,6 +369,154 @@ class PostNormBlock:
         return RowsInfo(norm=STREAM_ROWS, h=h)
 
 
+class HyperConnection:
+    """What ties one sublayer to the ``streams`` copies X_s of the stream: it reads u = sum_s a[s] X_s and, with its
+    output y, X_t <- sum_s C[s, t] X_s + m b[t] y for all t at once.  a (``.in``), b (``.out``) [streams] and C (``.mix``)
+    [streams, streams], indexed [from, to], are stored tensors under ``stem``; without a stem they are ones and the unit
+    matrix.  They stay on the device as float32: a recorded step reads them there."""
+
+    def __init__(self, streams: int, stem, rt):
+        self.S, self.stem, self.rt = int(streams), stem, rt
+        self.a = self.b = self.C = None
+
+    def plan(self) -> Dict[str, TensorSpec]:
+        if self.stem is None:
+            return {}
+        S = self.S
+        return {f"{self.stem}.in": TensorSpec((S,), init="mean", std=0.1), f"{self.stem}.out": TensorSpec((S,), init="ones_normal", std=0.1),
+                f"{self.stem}.mix": TensorSpec((S, S), init="eye_normal", std=0.1)}
+
+    def load(self, tensors) -> None:
+        rt, S = self.rt, self.S
+        if self.stem is None:
+            self.a = rt.vector(torch.ones(S))
+            self.b = rt.vector(torch.ones(S))
+            self.C = rt.vector(torch.eye(S))
+            return
+        self.a, self.b = rt.vector(tensors[f"{self.stem}.in"]), rt.vector(tensors[f"{self.stem}.out"])
+        self.C = rt.vector(tensors[f"{self.stem}.mix"])
+
+    def state(self) -> Dict[str, torch.Tensor]:
+        if self.stem is None:
+            return {}
+        return {f"{self.stem}.in": self.a, f"{self.stem}.out": self.b, f"{self.stem}.mix": self.C}
+
+    def nbytes(self) -> int:
+        return (2 * self.S + self.S * self.S) * 4
+
+
+class HyperBlock:
+    """Hyper-connections: ``streams`` copies X_1 .. X_S of the stream, [rows, S, hidden] float32, instead of one.  For
+    the mixer and then for the feed-forward (which may be absent), each with a ``HyperConnection`` (a, b, C) and a norm:
+        u = sum_s a[s] X_s;   y = sublayer(norm(u));   X_t <- sum_s C[s, t] X_s + m b[t] y    (all t from the old X)
+    with the spec's ``residual_mult`` m.  One stream with a = b = C = 1 is the pre-norm layer x += m sublayer(norm(x)).
+    The sublayers hand their output over as float32 rows (``produce``).  One kernel (``hyper_connect``) writes a
+    sublayer's output into the streams and forms the next reader's sum and norm from the new rows, so a layer is
+    two such launches beside its sublayers'; the first reader of the first layer takes the streams from the embedding's
+    rows in the same way."""
+
+    def __init__(self, spec, layer: int, rt):
+        if spec.streams < 1 or spec.streams > 8:
+            raise ValueError(f"layer {layer}: {spec.streams} streams (1 to 8 are taken)")
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.S, self.mult = int(spec.streams), float(spec.residual_mult)
+        self.mixer_norm = build_norm(spec.mixer_norm, rt)
+        self.mixer = build_mixer(spec.mixer, layer, rt)
+        stem = lambda key: f"{spec.prefix}{spec.names[key]}" if key in spec.names else None
+        self.mixer_hc = HyperConnection(self.S, stem("mixer_hc"), rt)
+        self.feed_forward = self.ffn_norm = self.ffn_hc = None
+        if spec.feed_forward is not None:
+            if spec.ffn_norm is None:
+                raise ValueError(f"layer {layer}: a feed-forward needs the norm in front of it")
+            self.ffn_norm = build_norm(spec.ffn_norm, rt)
+            self.feed_forward = build_feed_forward(spec.feed_forward, layer, rt)
+            self.ffn_hc = HyperConnection(self.S, stem("ffn_hc"), rt)
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and not hasattr(part, "produce"):
+                raise ValueError(f"layer {layer}: {type(part).__name__} offers no produce(); a hyper block needs a sublayer's "
+                                 f"output as rows of its own")
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and (getattr(norm, "spec", None) is None or norm.spec.kind != "rmsnorm"):
+                raise ValueError(f"layer {layer}: a hyper block's norms are of kind 'rmsnorm' (the kernel that sums the streams applies them)")
+
+    def _named(self):
+        s = self.spec
+        sfx = s.names.get("suffix", ".weight")
+        out = [(self.mixer_norm, (f"{s.prefix}{s.names['mixer_norm']}{sfx}",)), (self.mixer, (s.prefix, s.names)), (self.mixer_hc, ())]
+        if self.feed_forward is not None:
+            out += [(self.ffn_norm, (f"{s.prefix}{s.names['ffn_norm']}{sfx}",)), (self.feed_forward, (s.prefix, s.names)), (self.ffn_hc, ())]
+        return out
+
+    def plan(self) -> Dict[str, TensorSpec]:
+        p: Dict[str, TensorSpec] = {}
+        for part, args in self._named():
+            p.update(part.plan(*args))
+        return p
+
+    def load(self, tensors) -> None:
+        for part, args in self._named():
+            part.load(tensors, *args)
+
+    def state(self) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        for part, args in self._named():
+            if not hasattr(part, "state"):
+                raise NotImplementedError(f"{type(part).__name__} of layer {self.layer} offers no state(): its tensors "
+                                          f"cannot be given back by name")
+            out.update(part.state(*args))
+        return out
+
+    def cache_requests(self, site: int) -> List[object]:
+        return list(self.mixer.cache_requests(site))
+
+    def scratch_row(self) -> int:
+        parts = [p for p in (self.mixer, self.feed_forward) if p is not None]
+        return max(int(getattr(p, "scratch_row", lambda: 0)()) for p in parts) + 2 * self.spec.mixer.hidden
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p, _ in self._named() if not isinstance(p, HyperConnection))
+
+    def nbytes(self) -> int:
+        return sum(p.nbytes() for p, _ in self._named())
+
+    @property
+    def reader(self):
+        """(a, norm) of the block's first sublayer: what the kernel that last writes the streams needs to form its input."""
+        return self.mixer_hc.a, self.mixer_norm
+
+    def _connect(self, xs, y, hc, reader):
+        """Write y through ``hc`` (None: nothing to write) and read for ``reader`` = (a, norm) (None: nothing to read);
+        returns the reader's normed rows in the activations' dtype."""
+        h = None
+        if reader is not None:
+            h = self.rt.empty(xs.shape[0], xs.shape[2])
+        self.rt.kernels.hyper_connect(xs, y, hc.C if hc is not None else None, hc.b if hc is not None else None, self.mult,
+                                      reader[0] if reader is not None else None, reader[1].weight if reader is not None else None,
+                                      reader[1].spec.eps if reader is not None else 0.0, h)
+        return h
+
+    def forward(self, xs: torch.Tensor, batch, cache, site: int, info=None, next_reader=None):
+        """``xs``: the streams [rows, S, hidden] float32, updated in place.  ``info``: a ``RowsInfo`` whose ``h`` holds this
+        block's first input where the kernel before formed it.  ``next_reader``: (a, norm) of whatever reads the streams
+        next (the next block's ``reader``, or ones and the final norm); its rows come back in a ``RowsInfo``."""
+        from .norm import RowsInfo
+        if xs.dim() != 3 or xs.shape[1] != self.S:
+            raise ValueError(f"layer {self.layer}: the streams are {tuple(xs.shape)}, expected [rows, {self.S}, hidden]")
+        if info is not None and getattr(info, "norm", None) is self.mixer_norm and info.h is not None:
+            h = info.h
+        else:
+            h = self._connect(xs, None, None, self.reader)
+        y = self.mixer.produce(h, batch, cache, site)
+        if self.feed_forward is None:
+            h = self._connect(xs, y, self.mixer_hc, next_reader)
+        else:
+            h = self._connect(xs, y, self.mixer_hc, (self.ffn_hc.a, self.ffn_norm))
+            y = self.feed_forward.produce(h, batch)
+            h = self._connect(xs, y, self.ffn_hc, next_reader)
+        return RowsInfo(norm=next_reader[1], h=h) if next_reader is not None else None
+
+
 STREAM_ROWS = object()      # a RowsInfo whose ``norm`` is this holds the stream itself in the activations' dtype
 
 
@@ -375,3 +524,4 @@ register_block("prenorm", PreNormBlock)
 register_block("postnorm", PostNormBlock)
 register_block("sandwich", SandwichBlock)
 register_block("parallel", ParallelBlock)
+register_block("hyper", HyperBlock)

@@ -79,4 +79,63 @@ class GatedMLP:
         return self.down.logits(self.gate_up.activated(h))
 
 
+class PlainMLP:
+    """An ungated feed-forward (kind ``mlp``): y = W_down act(W_up h), act by the spec's ``activation``: one of the gate
+    activations of ``kernels.ACTIVATIONS`` or ``relu2`` (the square of ReLU).  The activation runs on the stored
+    projection (the activations' dtype), in float32 inside the kernel."""
+
+    def __init__(self, spec, layer: int, rt):
+        from ..kernels import UNGATED_ACTIVATIONS
+        if spec.activation not in UNGATED_ACTIVATIONS:
+            raise ValueError(f"mlp: activation '{spec.activation}' is not one of {sorted(UNGATED_ACTIVATIONS)}")
+        if spec.bias:
+            raise ValueError("mlp: biases are not implemented")
+        self.act = UNGATED_ACTIVATIONS[spec.activation]
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.up = self.down = None
+
+    @staticmethod
+    def _names(prefix: str, names: Dict[str, str]):
+        sfx = names.get("suffix", ".weight")
+        return tuple(f"{prefix}{names[k]}{sfx}" for k in ("up", "down"))
+
+    def plan(self, prefix: str, names: Dict[str, str]) -> Dict[str, TensorSpec]:
+        s = self.spec
+        up, down = self._names(prefix, names)
+        return {up: TensorSpec((s.intermediate, s.hidden)), down: TensorSpec((s.hidden, s.intermediate))}
+
+    def load(self, tensors, prefix: str, names: Dict[str, str]) -> None:
+        up, down = self._names(prefix, names)
+        self.up = Linear(tensors[up], None, self.rt)
+        self.down = Linear(tensors[down], None, self.rt)
+
+    def nbytes(self) -> int:
+        return self.up.nbytes() + self.down.nbytes()
+
+    def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
+        up, down = self._names(prefix, names)
+        return {up: self.up.weight, down: self.down.weight}
+
+    def scratch_row(self) -> int:
+        return self.spec.intermediate
+
+    graph_safe = True
+
+    def _middle(self, h) -> torch.Tensor:
+        if hasattr(h, "tensor"):
+            h = h.tensor()
+        z = self.up.store(h)
+        self.rt.kernels.activate(z, self.act)
+        return z
+
+    def forward(self, h, x: torch.Tensor, batch, next_norm=None):
+        self.down.accumulate(self._middle(h), x)
+        return None
+
+    def produce(self, h, batch) -> torch.Tensor:
+        """The feed-forward's output as float32 rows of its own (what ``forward`` adds into x)."""
+        return self.down.logits(self._middle(h))
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("mlp", PlainMLP)

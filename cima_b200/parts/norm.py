@@ -1,5 +1,6 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, computed in float32 from the float32 residual stream
-(src/kernels.cu:37-50).  ``size`` and ``eps`` come from the spec."""
+(src/kernels.cu:37-50).  ``size`` and ``eps`` come from the spec; with ``params["offset"]`` c the stored tensor w
+multiplies as c + w (a weight kept around zero: c = 1), formed once at load in float32."""
 from __future__ import annotations
 
 from typing import Dict
@@ -44,19 +45,24 @@ class NormedInput:
 class RMSNorm:
     def __init__(self, spec, rt):
         self.spec, self.rt = spec, rt
-        self.weight = None
+        self.offset = float(spec.params.get("offset", 0.0)) if spec.params else 0.0
+        self.weight = None                       # offset + the stored tensor: what the kernels multiply by
 
     def plan(self, name: str) -> Dict[str, TensorSpec]:
+        if self.offset:
+            return {name: TensorSpec((self.spec.size,), std=0.1)}
         return {name: TensorSpec((self.spec.size,), init="ones_normal")}
 
     def load(self, tensors: Dict[str, torch.Tensor], name: str) -> None:
         self.weight = self.rt.vector(tensors[name])
+        if self.offset:
+            self.weight = self.weight + self.offset
 
     def nbytes(self) -> int:
         return self.weight.numel() * 4
 
     def state(self, name: str) -> Dict[str, torch.Tensor]:
-        return {name: self.weight}
+        return {name: self.weight - self.offset if self.offset else self.weight}
 
     graph_safe = True
 

@@ -7,9 +7,16 @@ sine and cosine are float32 on the device).  With ``params["scaling"]`` = {facto
 frequencies are rescaled by their wavelength l = 2 pi / f: kept where l < original / high, divided by ``factor`` where
 l > original / low, and between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
 With ``params["linear"]`` = c every frequency is divided by c (positions compressed by c).
+With ``params["yarn"]`` = {factor c, original L, fast, slow} the frequencies are blended by their index: with
+d(z) = rotary_dim ln(L / (2 pi z)) / (2 ln theta), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and
+g_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i <- g_i f_i / c + (1 - g_i) f_i; and sine and cosine are multiplied
+by ``amplitude`` = 0.1 ln(c) + 1 (1 without "yarn"), which the rotating kernels take beside the table.
+``params["interleaved"]``: the pairs are neighbours (2i, 2i + 1) instead of (i, i + rotary_dim / 2).  A score q . k does
+not change when q and k are permuted alike, so a mixer whose kernels rotate half-split pairs permutes the rows of its
+query and key projections at load (``to_half_split``); kernels that take the layout as a flag are given ``interleaved``.
 ``none``: nothing rotates.
-A position part offers ``inv_freq`` (float32 [rotary_dim / 2]) and ``rotary_dim``; the attention
-mixer hands both to the kernel that rotates and appends.
+A position part offers ``inv_freq`` (float32 [rotary_dim / 2]), ``rotary_dim``, ``amplitude`` and ``interleaved``; the
+attention mixer hands them to the kernel that rotates and appends.
 """
 from __future__ import annotations
 
@@ -37,7 +44,23 @@ class Rope:
             if float(linear) <= 0:
                 raise ValueError(f"rope: the linear factor {linear} must be positive")
             inv = inv / float(linear)
+        self.amplitude = 1.0
+        yarn = spec.params.get("yarn") if spec.params else None
+        if yarn:
+            inv, self.amplitude = rescale_by_index(inv, float(spec.theta), float(yarn["factor"]), float(yarn["original"]),
+                                                   float(yarn["fast"]), float(yarn["slow"]))
+        self.interleaved = bool(spec.params.get("interleaved", False)) if spec.params else False
         self.inv_freq = inv.to(torch.float32).to(rt.device).contiguous()
+
+    def to_half_split(self, heads: int, head_dim: int) -> torch.Tensor:
+        """Row order that turns a projection whose heads rotate neighbouring pairs into one whose heads rotate the pairs
+        (i, i + rotary_dim / 2): new row h * head_dim + j is old row h * head_dim + order[j].  The identity where the
+        layout is half-split already."""
+        r = self.rotary_dim
+        one = list(range(head_dim))
+        if self.interleaved:
+            one = list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, head_dim))
+        return torch.tensor([h * head_dim + j for h in range(heads) for j in one], dtype=torch.long)
 
 
 def rescale_by_wavelength(inv: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
@@ -50,7 +73,27 @@ def rescale_by_wavelength(inv: torch.Tensor, factor: float, low: float, high: fl
     return torch.where(wave < original / high, inv, torch.where(wave > original / low, inv / factor, blended))
 
 
+def rescale_by_index(inv: torch.Tensor, theta: float, factor: float, original: float, fast: float, slow: float):
+    """(frequencies (float64) blended by their index as described at the top of this file, the factor of sine and cosine)."""
+    if factor <= 0 or original <= 0 or fast <= 0 or slow <= 0 or theta <= 1:
+        raise ValueError(f"rope yarn: factor {factor}, original {original}, fast {fast} and slow {slow} must be positive, theta {theta} above 1")
+    r = 2 * inv.numel()
+
+    def index_of(turns: float) -> float:
+        return r * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(index_of(fast)), 0)
+    hi = min(math.ceil(index_of(slow)), r - 1)
+    g = ((torch.arange(inv.numel(), dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return g * inv / factor + (1.0 - g) * inv, 0.1 * math.log(factor) + 1.0
+
+
 class NoPosition:
+    amplitude, interleaved = 1.0, False
+
+    def to_half_split(self, heads: int, head_dim: int) -> torch.Tensor:
+        return torch.arange(heads * head_dim, dtype=torch.long)
+
     def __init__(self, spec, rt):
         self.spec = spec
         self.rotary_dim = 0

@@ -29,7 +29,7 @@ from .safetensors_io import open_model_files
 class TensorSpec:
     shape: Tuple[int, ...]
     init: str = "normal"        # random-weights mode: "normal" N(0, std) | "ones_normal" 1 + N(0, std) | "mean" (1 + N(0, std)) / count
-                                # | "unit" uniform in (0, 1)
+                                # | "unit" uniform in (0, 1) | "eye_normal" the unit matrix + N(0, std)
     std: float = 0.02
 
 

@@ -32,7 +32,7 @@ def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, 
     """The tensor ``name`` drawn from the generator seeded by (seed, name), in slabs of ``_SLAB`` values in float32
     that are rounded into ``dtype`` as they come.  On the CPU a slab (a multiple of 16 values) continues the
     generator's sequence exactly where the last one ended, so the values do not depend on the slab size."""
-    if spec.init not in ("normal", "ones_normal", "mean", "unit"):
+    if spec.init not in ("normal", "ones_normal", "mean", "unit", "eye_normal"):
         raise ValueError(f"unknown init '{spec.init}' for tensor '{name}'")
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
@@ -52,6 +52,8 @@ def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, 
         if spec.init == "mean":                      # weights of an average: (1 + N(0, std)) / count
             part /= float(n)
         flat[lo:lo + part.numel()].copy_(part)
+    if spec.init == "eye_normal":                    # a square matrix around the unit matrix
+        out += torch.eye(spec.shape[0], spec.shape[1], dtype=dtype, device=device)
     return out
 
 

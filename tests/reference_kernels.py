@@ -139,7 +139,7 @@ class ReferenceKernels:
         qkv.copy_(y.to(qkv.dtype))
 
     def rope_append(self, qkv, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim,
-                    v_heads=None, qk_norm=None):
+                    v_heads=None, qk_norm=None, amplitude=1.0):
         T = qkv.shape[0]
         half = rotary_dim // 2
         nv = n_kv_heads if v_heads is None else v_heads
@@ -154,7 +154,7 @@ class ReferenceKernels:
             rot[..., :nd] = part
         if half:
             ang = (row_pos[:T].to(torch.float32)[:, None] * inv_freq[None, :]).to(self.compute)
-            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            c, s = torch.cos(ang)[:, None, :] * amplitude, torch.sin(ang)[:, None, :] * amplitude
             a, b = rot[..., :half].clone(), rot[..., half:rotary_dim].clone()
             rot[..., :half] = a * c - b * s
             rot[..., half:rotary_dim] = a * s + b * c
@@ -170,12 +170,12 @@ class ReferenceKernels:
             kv.storage[page, 1, :nv, off, :] = heads[r, n_heads + n_kv_heads:, :]
 
     def attention(self, qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, from_cache, after_append=False,
-                  sink=0.0, keep_first=0, v_group=1):
+                  sink=0.0, keep_first=0, v_group=1, head_sink=None):
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
-                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink, keep_first, v_group)
+                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink, keep_first, v_group, head_sink)
 
     def attention_plain(self, qkv, kv, row_pos, row_seq, seq_slot, seq_first_row, out, n_heads, n_kv_heads,
-                        head_dim, scale, window, from_cache, sink=0.0, keep_first=0, v_group=1):
+                        head_dim, scale, window, from_cache, sink=0.0, keep_first=0, v_group=1, head_sink=None):
         T = qkv.shape[0]
         rep = n_heads // n_kv_heads
         vplane = int(getattr(kv, "planes", 2)) - 1 if from_cache else 1      # one plane: the values are the keys
@@ -203,7 +203,12 @@ class ReferenceKernels:
             for h in range(n_heads):
                 g = h // rep
                 s = (k[:, g, :] @ q[h]) * scale
-                if sink:                                    # entries of score 0 without a value in the denominator
+                if head_sink is not None:                   # one entry of the head's own score without a value
+                    z = head_sink[h].to(self.compute)
+                    m = torch.maximum(s.max(), z)
+                    e = torch.exp(s - m)
+                    w = e / (e.sum() + torch.exp(z - m))
+                elif sink:                                  # entries of score 0 without a value in the denominator
                     m = torch.clamp(s.max(), min=0.0)
                     e = torch.exp(s - m)
                     w = e / (e.sum() + sink * torch.exp(-m))
@@ -287,18 +292,98 @@ def _latent_append(self, raw, g, eps, kv, batch):
         kv.storage[page, 0, 0, off, :] = c[t].to(kv.storage.dtype)
 
 
-def _head_linear(self, a, w, out, append=None):
+def _head_linear(self, a, w, out, append=None, a_head=None, out_head=None):
     if append is not None:
         self.latent_append(*append)
     heads, N, K = w.shape
-    y = torch.einsum("thk,hnk->thn", a.reshape(a.shape[0], heads, K).to(self.compute), w.to(self.compute))
-    out.copy_(y.reshape(a.shape[0], heads * N).to(out.dtype))
+    ha, ho = a_head or K, out_head or N
+    T = a.shape[0]
+    av = torch.stack([a[:, h * ha:h * ha + K] for h in range(heads)], dim=1)
+    y = torch.einsum("thk,hnk->thn", av.to(self.compute), w.to(self.compute)).to(out.dtype)
+    for h in range(heads):
+        out[:, h * ho:h * ho + N] = y[:, h]
+
+
+def _turn_pairs(x, pos, inv_freq, amplitude, interleaved, compute):
+    """x [..., rot] rotated at positions pos (broadcast over the leading dims of x): pairs of neighbours or of halves."""
+    rot = x.shape[-1]
+    half = rot // 2
+    ang = (pos.to(torch.float32)[..., None] * inv_freq).to(compute)
+    c, s = torch.cos(ang) * amplitude, torch.sin(ang) * amplitude
+    x = x.to(compute)
+    out = torch.empty_like(x)
+    if interleaved:
+        a, b = x[..., 0::2], x[..., 1::2]
+        out[..., 0::2], out[..., 1::2] = a * c - b * s, b * c + a * s
+    else:
+        a, b = x[..., :half], x[..., half:]
+        out[..., :half], out[..., half:] = a * c - b * s, b * c + a * s
+    return out
+
+
+def _latent_prepare(self, ql, first, q_norm, cq, c_norm, eps, rank, rot, inv_freq, amplitude, interleaved, kv, batch, step_rows=None):
+    T = ql.shape[0]
+    r = ql.to(self.compute)
+    if cq is not None:
+        p = r[:, :first]
+        cq.copy_((p / torch.sqrt((p * p).mean(-1, keepdim=True) + eps) * q_norm.to(self.compute)).to(cq.dtype))
+    p = r[:, first:first + rank]
+    both = torch.empty((T, rank + rot), dtype=ql.dtype)
+    both[:, :rank] = (p / torch.sqrt((p * p).mean(-1, keepdim=True) + eps) * c_norm.to(self.compute)).to(ql.dtype)
+    if rot:
+        both[:, rank:] = _turn_pairs(ql[:, first + rank:first + rank + rot], batch.row_pos[:T], inv_freq, amplitude, interleaved,
+                                     self.compute).to(ql.dtype)
+    for t in range(T):
+        seq = int(batch.row_seq[t])
+        if kv.ring_pages and int(batch.row_pos[t]) + kv.ring_pages * kv.page_size < int(batch.seq_len[seq]):
+            continue
+        page, off = _page_offset(kv, int(batch.seq_slot[seq]), int(batch.row_pos[t]))
+        kv.storage[page, 0, 0, off, :] = both[t]
+    if step_rows is not None:
+        buf, col = step_rows
+        buf[:, col:col + rank + rot] = both
+        buf[:, col + rank + rot:col + 2 * (rank + rot)] = both
+
+
+def _rope_rows(self, q, q_off, q_head, out, o_off, o_head, heads, rot, inv_freq, amplitude, interleaved, row_pos):
+    T = q.shape[0]
+    for h in range(heads):
+        part = q[:, h * q_head + q_off:h * q_head + q_off + rot]
+        out[:, h * o_head + o_off:h * o_head + o_off + rot] = _turn_pairs(part, row_pos[:T], inv_freq, amplitude, interleaved,
+                                                                         self.compute).to(out.dtype)
+
+
+def _hyper_connect(self, xs, y, C, b, mult, a_next, w_next, eps, h, spread=False):
+    T, S, W = xs.shape
+    if y is not None:
+        if spread:
+            xs.copy_(y[:, None, :].expand(T, S, W))
+        else:
+            new = torch.einsum("st,xsw->xtw", C.view(S, S), xs) + mult * b.view(1, S, 1) * y[:, None, :]
+            xs.copy_(new)
+    if a_next is not None:
+        u = torch.einsum("s,xsw->xw", a_next, xs)
+        h.copy_((u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * w_next).to(h.dtype))
+
+
+def _activate(self, z, act):
+    f = z.float()
+    z.copy_((torch.clamp(f, min=0.0) ** 2 if act == 5 else self.gate_act(f, act)).to(z.dtype))
+
+
+def _gate_rows(self, z, g, col):
+    z.copy_((z.float() * torch.sigmoid(g[:, col:col + 1])).to(z.dtype))
 
 
 ReferenceKernels.short_conv = _short_conv
 ReferenceKernels.depth_average = _depth_average
 ReferenceKernels.latent_append = _latent_append
 ReferenceKernels.head_linear = _head_linear
+ReferenceKernels.latent_prepare = _latent_prepare
+ReferenceKernels.rope_rows = _rope_rows
+ReferenceKernels.hyper_connect = _hyper_connect
+ReferenceKernels.activate = _activate
+ReferenceKernels.gate_rows = _gate_rows
 
 
 # ---------------------------------------------------------------------- Dynamic Tanh, bigram embedding
@@ -403,22 +488,24 @@ def _rms_mean(self, ys, ws, x, eps, assign=False):
 
 
 # ---------------------------------------------------------------------- routed feed-forward
-def _moe_route(self, scores, top, groups, keep, scale, idx, wgt):
-    T, E = scores.shape
+def _moe_route(self, scores, top, groups, keep, scale, idx, wgt, experts=None, softmax=False, correction=None):
+    T = scores.shape[0]
+    E = scores.shape[1] if experts is None else experts
     per = E // groups
-    s = torch.sigmoid(scores)
+    s = torch.softmax(scores[:, :E], dim=-1) if softmax else torch.sigmoid(scores[:, :E])
+    cmp = s if correction is None else s + correction
     for t in range(T):
-        gs = [float(s[t, gi * per:(gi + 1) * per].topk(min(2, per)).values.sum()) for gi in range(groups)]
+        gs = [float(cmp[t, gi * per:(gi + 1) * per].topk(min(2, per)).values.sum()) for gi in range(groups)]
         best = sorted(range(groups), key=lambda gi: (-gs[gi], gi))[:keep]
         allowed = [e for gi in best for e in range(gi * per, (gi + 1) * per)]
-        chosen = sorted(allowed, key=lambda e: (-float(s[t, e]), e))[:top]
+        chosen = sorted(allowed, key=lambda e: (-float(cmp[t, e]), e))[:top]
         w = torch.stack([s[t, e] for e in chosen])
         idx[t] = torch.tensor(chosen, dtype=idx.dtype)
         wgt[t] = w / (w.sum() + 1e-20) * scale
-    scores.copy_(s)
+    scores[:, :E] = s
 
 
-def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False):
+def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False, limit=0.0):
     ff = gate_up.shape[1] // 2
     hf = h.float()
     for t in range(h.shape[0]):
@@ -426,7 +513,7 @@ def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False):
         for j in range(idx.shape[1]):
             e = int(idx[t, j])
             gu = (gate_up[e].float() @ hf[t]).to(h.dtype).float()
-            z = (self.gate_act(gu[:ff], act) * gu[ff:]).to(h.dtype).float()
+            z = self.gated(gu[:ff], gu[ff:], act, limit).to(h.dtype).float()
             acc = acc + wgt[t, j] * (down[e].float() @ z)
         x[t] = acc if assign else x[t] + acc
 
