@@ -115,6 +115,29 @@ def folder(name: str, seed: int = 0, sharp: bool = True) -> str:
     return _FOLDERS[key]
 
 
+def variant_folder(name: str, edit, seed: int = 0, sharp: bool = True) -> str:
+    """A folder of configuration ``name`` after ``edit(cfg)`` changed constants in it (masks, multipliers): tensors are drawn
+    by name, so the weights are those of the unchanged configuration."""
+    import copy
+    cfg = copy.deepcopy(CONFIGS[name])
+    edit(cfg)
+    return write_folder(tempfile.mkdtemp(prefix=f"cima_netezen_{name}_variant_"), cfg, seed, sharp)
+
+
+def carrying_edge(cfg, W, toks, layer: int, key: str, candidates):
+    """Among ``candidates`` for the mask constant ``key`` of ``layer``, the value v whose step to v - 1 changes the last
+    row of the plain implementation's logits most: at v a key that carries that row is just visible, at v - 1 just not."""
+    import copy
+    from netezen_plain import plain_forward
+    rows = {}
+    for v in sorted(set(candidates) | {c - 1 for c in candidates}):
+        c2 = copy.deepcopy(cfg)
+        c2["layers"][layer]["mixer"]["mask"][key] = v
+        rows[v] = plain_forward(c2, W, toks)[-1]
+    best = max(candidates, key=lambda v: float((rows[v] - rows[v - 1]).abs().max()))
+    return best, float((rows[best] - rows[best - 1]).abs().max())
+
+
 def plain_weights(name: str, seed: int = 0, sharp: bool = True):
     """(config dict, tensors in float64) of a folder, read without the package."""
     from netezen_plain import read_folder

@@ -22,7 +22,7 @@ The design in this file's notation (T tokens of one sequence, width W, t a posit
         f_i <- g_i f_i / c + (1 - g_i) f_i, and sine and cosine are multiplied by 0.1 ln(c) + 1.
   mixer "attention":  q, k, v projected without bias; query head h reads key head h // (H / G); q and k rotated;
         key j is seen from i when j <= i and (i - j < size or j < keep_first); softmax(q . k * scale) v; W_o.
-  mixer "latent_attention":  c_q = rms(W_dq h) * w_q,  q = W_uq c_q, a head = [dim plain | rot_dim rotated];
+  mixer "latent_attention":  c_q = rms(W_dq h) * w_q,  q = W_uq c_q (with q_rank 0: q = W_q h), a head = [dim plain | rot_dim rotated];
         W_dkv h = [kv_rank | rot_dim]: c = rms(first part) * w_c, the second part rotated is one key part for all heads;
         head h: k = [W_uk[h] c | shared rotated part], v = W_uv[h] c;  key j is seen from i when 0 <= i - j < size;
         p_j = exp(s_j) / (exp(sink_h) + sum_j' exp(s_j')),  s = q . k * scale;  W_o.
@@ -144,8 +144,11 @@ def plain_latent_attention(h: torch.Tensor, W: dict, m: dict, eps: float) -> tor
     "dkv", "dkv.norm", "uk", "uv", "sink", "o"."""
     T = h.shape[0]
     H, D, R, V, C = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
-    cq = plain_rms(h @ W["dq"].T, eps) * W["dq.norm"]
-    q = (cq @ W["uq"].T).reshape(T, H, D + R)
+    if int(m.get("q_rank", 0)):
+        cq = plain_rms(h @ W["dq"].T, eps) * W["dq.norm"]
+        q = (cq @ W["uq"].T).reshape(T, H, D + R)
+    else:                                                        # no query latent: the queries straight from the input
+        q = (h @ W["q"].T).reshape(T, H, D + R)
     both = h @ W["dkv"].T
     c = plain_rms(both[:, :C], eps) * W["dkv.norm"]
     rot = dict(m["rot"], dims=R)
