@@ -231,7 +231,7 @@ def main(argv=None) -> int:
                     "defined on the default, Qwen2.5-7B)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--design", default=None, choices=["vunovik", "gisirax", "lipizen"], help="instead of the metric line: decode and prefill "
+    ap.add_argument("--design", default=None, choices=["vunovik", "gisirax", "lipizen", "netezen"], help="instead of the metric line: decode and prefill "
                     "throughput of that design's shapes beside the Qwen2 shape of equal size (--sizes, --layers)")
     ap.add_argument("--sizes", default="1.5b,3b,7b", help="with --design: the shapes to measure (0.5b, 1.5b, 3b, 7b)")
     ap.add_argument("--per-kernel", action="store_true", help="instead of the metric line: every launch of one decode step "

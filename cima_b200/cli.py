@@ -26,7 +26,7 @@ from typing import List
 from .sampling.options import GenOptions, OptionError, render_help
 
 USAGE = """\
-cima_b200 — generation library for the Qwen2 dense decoder and the Vunovik, Gisirax and Lipizen decoders on one B200
+cima_b200 — generation library for the Qwen2 dense decoder and the Vunovik, Gisirax, Lipizen and Netezen decoders on one B200
 
 Usage:
   cima run <MODEL_DIR> [TOKEN_ID ...]   Generate from a prompt of token ids (--prompts FILE: one per line)

@@ -5,6 +5,10 @@ widths: two delta-rule layers, then one layer of softmax attention beside a deca
 experts of which a token uses as many values of a feed-forward's middle as the Qwen2 shape has, and shapes of the
 Lipizen decoder at those widths: of every four layers one runs the gate recurrence and three differential attention (the
 last of them on the keys and values of the one before it), every layer with the dense feed-forward of the Qwen2 shape.
+And shapes of the Netezen decoder at those widths: two copies of the stream; layers alternate between latent attention
+(a position keeps 96 + 32 values) and grouped-query attention with the Qwen2 shape's heads behind a window that keeps first
+positions; the first layer's feed-forward is the ungated one, the others route 3 of 16 clamped experts beside a shared
+one, a token using as many values of a middle as the Qwen2 shape has.
 Every entry is a complete config.json; nothing here is read by the model code."""
 
 
@@ -67,12 +71,39 @@ def _lipizen(layers, width, heads, kv_heads, dim, ff, vocab, taps=4, window=1024
             "logit_softcap": 30.0, "layers": out}
 
 
-# the Qwen2 shape that a Vunovik, Gisirax or Lipizen shape is measured beside
-TWINS = {"lipizen-0.5b": "qwen2.5-0.5b", "lipizen-1.5b": "qwen2.5-1.5b", "lipizen-3b": "qwen2.5-3b", "lipizen-7b": "qwen2.5-7b",
+def _netezen(layers, width, heads, kv_heads, dim, ff, vocab, experts=16, top=3, window=1024, keep_first=64, rank=96, rot=32, streams=2):
+    """Even layers: latent attention with ``heads`` heads of ``dim - rot`` plain and ``rot`` rotated values; odd layers:
+    grouped-query attention.  ``top`` routed experts and the shared one have ``ff / (top + 1)`` values each."""
+    per = -(-ff // (top + 1) // 64) * 64
+    moe = {"kind": "moe", "expert": {"ff": per, "limit": 7.0}, "router": {"experts": experts, "top": top}, "shared": {"ff": per, "limit": 7.0}}
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": -(-(3 * ff // 2) // 64) * 64} if i == 0 else moe
+        if i % 2 == 0:
+            mixer = {"heads": heads, "dim": dim - rot, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "q_rank": max(64, width // 4 // 64 * 64),
+                     "scale": dim ** -0.5, "rot": {"dims": rot, "base": 10000.0}, "mask": {"size": window}}
+            out.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "rot": {"dims": dim // 2, "base": 1000000.0, "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}},
+                     "mask": {"size": window, "keep_first": keep_first}}
+            out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Netezen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": streams,
+            "layers": out}
+
+
+# the Qwen2 shape that a Vunovik, Gisirax, Lipizen or Netezen shape is measured beside
+TWINS = {"netezen-0.5b": "qwen2.5-0.5b", "netezen-1.5b": "qwen2.5-1.5b", "netezen-3b": "qwen2.5-3b", "netezen-7b": "qwen2.5-7b",
+         "lipizen-0.5b": "qwen2.5-0.5b", "lipizen-1.5b": "qwen2.5-1.5b", "lipizen-3b": "qwen2.5-3b", "lipizen-7b": "qwen2.5-7b",
          "gisirax-0.5b": "qwen2.5-0.5b", "gisirax-1.5b": "qwen2.5-1.5b", "gisirax-3b": "qwen2.5-3b", "gisirax-7b": "qwen2.5-7b",
          "vunovik-0.5b": "qwen2.5-0.5b", "vunovik-1.5b": "qwen2.5-1.5b", "vunovik-3b": "qwen2.5-3b", "vunovik-7b": "qwen2.5-7b"}
 
 SHAPES = {
+    "netezen-tiny": _netezen(4, 128, 4, 2, 32, 256, 512, experts=6, top=2, window=96, keep_first=4, rank=48, rot=16),
+    "netezen-0.5b": _netezen(24, 896, 14, 2, 64, 4864, 151936, rank=96, rot=32),
+    "netezen-1.5b": _netezen(28, 1536, 12, 2, 128, 8960, 151936),
+    "netezen-3b": _netezen(36, 2048, 16, 2, 128, 11008, 151936),
+    "netezen-7b": _netezen(28, 3584, 28, 4, 128, 18944, 152064),
     "lipizen-tiny": _lipizen(4, 128, 4, 2, 32, 256, 512, taps=3, window=96, keep_first=4),
     "lipizen-0.5b": _lipizen(24, 896, 14, 2, 64, 4864, 151936),
     "lipizen-1.5b": _lipizen(28, 1536, 12, 2, 128, 8960, 151936),

@@ -44,6 +44,9 @@ class Attention:
                              f"where the projections have biases (heads are padded in the cache only without biases)")
         self.spec, self.layer, self.rt = spec, layer, rt
         self.position = build_position(spec.position, rt)
+        # (a position part registered elsewhere may offer neither: half-split pairs, amplitude 1)
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
+        self.amplitude = float(getattr(self.position, "amplitude", 1.0))
         self.qd = spec.n_heads * self.hd
         self.kvd = spec.n_kv_heads * self.hd
         self.qkv = None
@@ -81,11 +84,11 @@ class Attention:
 
         def rows(k):
             t = tensors[f"{prefix}{names[k]}{sfx}"]
-            if k != "v" and self.position.interleaved:
+            if k != "v" and self.interleaved:
                 t = t[self.position.to_half_split(sizes[k][0], self.dim).to(t.device)]
             return self._pad_rows(t, *sizes[k])
 
-        if self.position.interleaved and s.qkv_bias:
+        if self.interleaved and s.qkv_bias:
             raise ValueError("attention: neighbouring rotary pairs with biases on q and k are not implemented")
         self.qkv = Linear([rows(k) for k in ("q", "k", "v")], bias, self.rt)
         ob = tensors[f"{prefix}{names['o']}.bias"] if s.out_bias else None
@@ -106,7 +109,7 @@ class Attention:
                                        ("v", self.kvd, s.n_kv_heads, self.vdim)):
             w = self.qkv.weight[r:r + rows]
             w = w if size == self.hd else w.view(heads, self.hd, -1)[:, :size].reshape(heads * size, -1)
-            if key != "v" and self.position.interleaved:
+            if key != "v" and self.interleaved:
                 order = self.position.to_half_split(heads, size).to(w.device)
                 back = torch.empty_like(w)
                 back[order] = w
@@ -157,7 +160,7 @@ class Attention:
         writes = s.cache_from is None
         rows = h.shape[0]
         if (not batch.prefill and writes and self.qkv._skinny(rows) and kv.storage.dtype is torch.bfloat16
-                and self.position.rotary_dim == self.hd and self.position.amplitude == 1.0 and hasattr(K_, "qkv_rope")):
+                and self.position.rotary_dim == self.hd and self.amplitude == 1.0 and hasattr(K_, "qkv_rope")):
             # decoding: projection, rotation and the append to the cache as one kernel
             qkv = self.rt.empty(rows, self.qd + 2 * self.kvd)
             if self.qkv._folds(h, rows):
@@ -170,10 +173,10 @@ class Attention:
                             s.n_kv_heads, self.hd)
         else:
             qkv = self.qkv.store(h)
-            if self.position.amplitude != 1.0:
+            if self.amplitude != 1.0:
                 K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
                                batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, self.hd,
-                               amplitude=self.position.amplitude)
+                               amplitude=self.amplitude)
             else:
                 K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
                                batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, self.hd)
