@@ -5,7 +5,8 @@
 //   moe_sort      the (row, choice) pairs ordered by expert: offsets of every expert's pairs and of its row tiles
 //   moe_gemm 0    z[i] = act(W_gate[e] h[row]) * (W_up[e] h[row])      for the sorted pairs i (a tile = 32 pairs of one expert)
 //   moe_gemm 1    y[pair] = W_down[e] z[i]                             float32, back at the pair's own place
-//   moe_combine   x[row] += sum_j weight[row, j] * y[row * top + j]    ascending j, float32
+//   moe_combine   x[row] += sum_j weight[row, j] * y[row * top + j]    ascending j, float32; a shared expert's rows (float32), times
+//                 the sigmoid of a gate logit a row where one is given, join the sum behind the chosen experts' 
 // A pair's sums run over k in ascending order with one accumulator, so its result does not depend on which other
 // rows share its tile, nor on the order in which the sort placed the pairs of an expert.
 //
@@ -236,16 +237,18 @@ k_moe_gemm(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __
 // pos: the row of y that holds pair (row, j), or null where y is kept by pair
 __global__ void __launch_bounds__(256)
 k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ pos, float* __restrict__ x,
-              int top, int H, int assign) {
+              int top, int H, int assign, const float* __restrict__ shared, const float* __restrict__ gate, int ldg) {
   cima_pdl_wait();
   cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   const size_t row = blockIdx.x;
+  const float sg = shared ? (gate ? 1.0f / (1.0f + expf(-gate[row * (size_t)ldg])) : 1.0f) : 0.f;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float s = 0.f;
     for (int j = 0; j < top; j++) {
       const size_t p = row * top + j;
       s = fmaf(wgt[p], y[(pos ? (size_t)pos[p] : p) * H + c], s);
     }
+    if (shared) s = fmaf(sg, shared[row * H + c], s);
     x[row * H + c] = assign ? s : x[row * H + c] + s;
   }
 }
@@ -444,9 +447,11 @@ extern "C" int cima_moe_gemm(const void* a, int adtype, int lda, const void* w, 
 }
 
 // y [pairs or places, H] float32; pos [T * top] the row of y of every pair, or null where y is kept by pair
-extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos, float* x, int T, int top, int H, int assign, cudaStream_t stream) {
+// shared (may be null): [T, H] float32 rows added behind the experts', each row times sigmoid(gate[row * ldg]) where gate is given
+extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos, float* x, int T, int top, int H, int assign,
+                                const float* shared, const float* gate, int ldg, cudaStream_t stream) {
   if (T <= 0) return 0;
-  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H, assign);
+  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H, assign, shared, gate, ldg);
   return rc ? rc : cima_launch_result();
 }
 

@@ -90,7 +90,7 @@ _SIGNATURES = {
     "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "cima_moe_sort": [_vp, _i, _i, _vp, _vp, _vp, _vp],
     "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp],
     "cima_moe_sort_tiles": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "cima_moe_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "cima_moe_few": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -103,7 +103,7 @@ _SIGNATURES = {
     "cima_rope_rows": [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _f, _i, _vp, _i, _vp],
     "cima_hyper_connect": [_vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "cima_activate": [_vp, _i, _sz, _i, _vp],
-    "cima_gate_rows": [_vp, _i, _i, _i, _vp, _i, _vp],
+
     "cima_head_linear_append": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp,
                                 _i, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _vp, _vp],
@@ -910,18 +910,6 @@ class Kernels:
         if not self._admit("activate", 2 * z.numel() * z.element_size()): return
         self._check(self.lib.cima_activate(z.data_ptr(), dtype_code(z.dtype), z.numel(), int(act), self._stream()), "activate")
 
-    def gate_rows(self, z: torch.Tensor, g: torch.Tensor, col: int) -> None:
-        """z[t, :] *= sigmoid(g[t, col]) in place: g float32 [T, n]."""
-        self._need(z, "z", None, 2); self._need(g, "g", torch.float32, 2)
-        T, N = z.shape
-        if g.shape[0] != T or not (0 <= col < g.shape[1]):
-            raise KernelError(f"gate_rows: g {tuple(g.shape)} has no column {col} for the {T} rows of z")
-        if T == 0:
-            return
-        if not self._admit("gate_rows", 2 * z.numel() * z.element_size()): return
-        self._check(self.lib.cima_gate_rows(z.data_ptr(), dtype_code(z.dtype), T, N, g[:, col:].data_ptr(), g.stride(0), self._stream()),
-                    "gate_rows")
-
     # ------------------------------------------------------------------ Dynamic Tanh, bigram embedding
     def dyt(self, x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
         """out = tanh(alpha * x) * w + b: x float32 [T, H], alpha one float32 value on the device, w and b [H]."""
@@ -1184,12 +1172,28 @@ class Kernels:
 
     def moe_experts(self, h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
                     x: torch.Tensor, act: int = 0, assign: bool = False, ordered: Optional[torch.Tensor] = None,
-                    limit: float = 0.0) -> None:
+                    limit: float = 0.0, shared=None) -> None:
         """x[t] += (with ``assign``: =) sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
         gate_up [E, 2 ff, H] (an expert's gate rows, then its up rows), down [E, H, ff]; x float32 [T, H].  Four launches:
         the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum.  The
         products take one of three roads by the step's size and dtype alone (``MOE_TC_PAIRS``, ``MOE_FEW_PAIRS``): tcgen05
-        tiles of 256 pairs, a warp a feature for the few pairs of a decode step, or the plain tiles (any dtype and size)."""
+        tiles of 256 pairs, a warp a feature for the few pairs of a decode step, or the plain tiles (any dtype and size).
+        ``limit`` goes with the clamped form of the middle.  ``shared = (rows, gate, col)``: float32 rows [T, H] (a shared
+        expert's output) that join the weighted sum in its launch, each row times sigmoid(gate[t, col]) (gate float32
+        [T, n]; None: unweighted)."""
+        tail = (None, None, 0)
+        if shared is not None:
+            srows, sgate, scol = shared
+            self._need(srows, "shared rows", torch.float32, 2)
+            if tuple(srows.shape) != tuple(x.shape):
+                raise KernelError(f"moe_experts: the shared rows are {tuple(srows.shape)}, expected {tuple(x.shape)}")
+            if sgate is not None:
+                self._need(sgate, "shared gate", torch.float32, 2)
+                if sgate.shape[0] != x.shape[0] or not (0 <= scol < sgate.shape[1]):
+                    raise KernelError(f"moe_experts: the shared gate {tuple(sgate.shape)} has no column {scol} for {x.shape[0]} rows")
+                tail = (srows.data_ptr(), sgate[:, scol:].data_ptr(), sgate.stride(0))
+            else:
+                tail = (srows.data_ptr(), None, 0)
         self._need(h, "h", None, 2); self._need(gate_up, "gate_up", None, 3); self._need(down, "down", gate_up.dtype, 3)
         self._need(idx, "idx", torch.int32, 2); self._need(wgt, "wgt", torch.float32, 2); self._need(x, "x", torch.float32, 2)
         T, H = h.shape
@@ -1203,7 +1207,7 @@ class Kernels:
         dev = h.device
         bf16 = h.dtype is torch.bfloat16 and gate_up.dtype is torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and h.stride(0) % 8 == 0
         if bf16 and P >= self.MOE_TC_PAIRS:
-            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act, assign, limit)
+            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act, assign, limit, tail)
         few = bf16 and P <= self.MOE_FEW_PAIRS
         meta = ordered if ordered is not None else torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
         offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
@@ -1232,12 +1236,13 @@ class Kernels:
                                                    y.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(), P, E, top,
                                                    H, ff, 1, 0, 0.0, self._stream()), "moe_gemm")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
-            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), None, x.data_ptr(), T, top, H, int(assign), self._stream()), "moe_combine")
+            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), None, x.data_ptr(), T, top, H, int(assign), *tail,
+                                                  self._stream()), "moe_combine")
 
     MOE_TC_PAIRS = 1024      # from this many (row, choice) pairs on, bfloat16 experts run on the tcgen05 tiles of 256 pairs
     MOE_FEW_PAIRS = 128      # up to this many, a warp computes a feature for the pairs of an expert (a decode step)
 
-    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act, assign=False, limit: float = 0.0) -> None:
+    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act, assign=False, limit: float = 0.0, tail=(None, None, 0)) -> None:
         """Many pairs in bfloat16: every expert's pairs are laid out from a multiple of 256 rows on (the rows of h copied
         there), so that each tile of the tcgen05 product multiplies with one expert's matrix."""
         T, H = h.shape
@@ -1269,7 +1274,7 @@ class Kernels:
                                                                 flag.data_ptr(), self._stream()), "gemm_tcgen05_pair_grouped")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
             self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), pos.data_ptr(), x.data_ptr(), T, top, H,
-                                                  int(assign), self._stream()), "moe_combine")
+                                                  int(assign), *tail, self._stream()), "moe_combine")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:

@@ -163,17 +163,16 @@ class RoutedExperts:
         wgt = rt.empty(rows, self.top, dtype=torch.float32)
         # (a decode step's few rows: the routing launch also orders the pairs by expert)
         small = rows <= getattr(K_, "ROUTE_SORT_ROWS", 0) and rows * self.top < getattr(K_, "MOE_TC_PAIRS", 0)
+        if self.shared_spec is not None:
+            # the shared expert's rows (float32) join the chosen experts' weighted sum in its launch, each row times the
+            # sigmoid of its gate logit (the last column of the routing product)
+            expert["shared"] = (self.shared_down.logits(self.shared_up.activated(h)), scores if self.shared_gate else None, self.E)
         if small:
             ordered = K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt, order=True, experts=self.E, **route)
             K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act, assign=assign, ordered=ordered, **expert)
         else:
             K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt, experts=self.E, **route)
             K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act, assign=assign, **expert)
-        if self.shared_spec is not None:
-            z = self.shared_up.activated(h)
-            if self.shared_gate:
-                K_.gate_rows(z, scores, self.E)                      # every row times the sigmoid of its gate logit
-            self.shared_down.accumulate(z, x)
 
 
 register_feed_forward("moe", RoutedExperts)

@@ -371,10 +371,6 @@ def _activate(self, z, act):
     z.copy_((torch.clamp(f, min=0.0) ** 2 if act == 5 else self.gate_act(f, act)).to(z.dtype))
 
 
-def _gate_rows(self, z, g, col):
-    z.copy_((z.float() * torch.sigmoid(g[:, col:col + 1])).to(z.dtype))
-
-
 ReferenceKernels.short_conv = _short_conv
 ReferenceKernels.depth_average = _depth_average
 ReferenceKernels.latent_append = _latent_append
@@ -383,7 +379,6 @@ ReferenceKernels.latent_prepare = _latent_prepare
 ReferenceKernels.rope_rows = _rope_rows
 ReferenceKernels.hyper_connect = _hyper_connect
 ReferenceKernels.activate = _activate
-ReferenceKernels.gate_rows = _gate_rows
 
 
 # ---------------------------------------------------------------------- Dynamic Tanh, bigram embedding
@@ -505,7 +500,7 @@ def _moe_route(self, scores, top, groups, keep, scale, idx, wgt, experts=None, s
     scores[:, :E] = s
 
 
-def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False, limit=0.0):
+def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False, limit=0.0, shared=None):
     ff = gate_up.shape[1] // 2
     hf = h.float()
     for t in range(h.shape[0]):
@@ -515,6 +510,9 @@ def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False, limit
             gu = (gate_up[e].float() @ hf[t]).to(h.dtype).float()
             z = self.gated(gu[:ff], gu[ff:], act, limit).to(h.dtype).float()
             acc = acc + wgt[t, j] * (down[e].float() @ z)
+        if shared is not None:
+            rows, gate, col = shared
+            acc = acc + (torch.sigmoid(gate[t, col]) if gate is not None else 1.0) * rows[t]
         x[t] = acc if assign else x[t] + acc
 
 

@@ -69,7 +69,7 @@ def test_streams_take_an_output_and_are_read(T, S, W, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_ungated_activations_and_a_gate_a_row(dtype):
+def test_ungated_activations(dtype):
     torch.manual_seed(1)
     for shape in ((3, 40), (70, 256), (5, 33)):
         z = (torch.randn(*shape) * 3).to(DT[dtype])
@@ -78,11 +78,6 @@ def test_ungated_activations_and_a_gate_a_row(dtype):
             R.activate(want, act)
             K().activate(got, act)
             assert close(got, want, tol_of(dtype))
-        g = torch.randn(shape[0], 7)
-        want, got = z.clone(), z.to(DEV)
-        R.gate_rows(want, g, 4)
-        K().gate_rows(got, g.to(DEV), 4)
-        assert close(got, want, tol_of(dtype))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -289,6 +284,14 @@ def test_clamped_experts_on_every_road(T, E, top, ff, H, dtype):
     got = torch.full((T, H), 3.0, device=DEV)
     K().moe_experts(h.to(DEV), gu.to(DEV), dn.to(DEV), idx.to(DEV), wgt.to(DEV), got, 4, assign=True, limit=1.5)
     assert close(got, want, 3e-5 if dtype == "float32" else 2.5e-2)
+    # a shared expert's rows, gated by a column of a wider matrix or not at all, join the sum in the same launch
+    rows, gate = torch.randn(T, H), torch.randn(T, E + 1)
+    for g_ in (gate, None):
+        want2 = want + (torch.sigmoid(gate[:, E:E + 1]) if g_ is not None else 1.0) * rows
+        got = torch.full((T, H), 3.0, device=DEV)
+        K().moe_experts(h.to(DEV), gu.to(DEV), dn.to(DEV), idx.to(DEV), wgt.to(DEV), got, 4, assign=True, limit=1.5,
+                        shared=(rows.to(DEV), g_.to(DEV) if g_ is not None else None, E))
+        assert close(got, want2, 3e-5 if dtype == "float32" else 2.5e-2)
 
 
 # ------------------------------------------------------------------------------------------- the model
