@@ -123,13 +123,13 @@ k_hyper_connect4(float* __restrict__ X, const float* __restrict__ y, const float
   for (int i = 0; i < S * S; i++) rC[i] = C ? C[i] : 0.f;
 #pragma unroll
   for (int i = 0; i < S; i++) { rb[i] = b ? mult * b[i] : 0.f; ra[i] = a ? a[i] : 0.f; }
-  const int W4 = W >> 2;
+  const int W4 = W >> 2, NT = blockDim.x;       // 128 threads where they cover the row in four groups, else 256
   const size_t row = blockIdx.x;
   // the norm's weight does not depend on the kernel before this one either
   float4 wv[HC_GROUPS];
 #pragma unroll
   for (int k = 0; k < HC_GROUPS; k++) {
-    const int g = threadIdx.x + k * HC_THREADS;
+    const int g = threadIdx.x + k * NT;
     wv[k] = (a && g < W4) ? reinterpret_cast<const float4*>(w)[g] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   cima_pdl_wait();
@@ -137,11 +137,11 @@ k_hyper_connect4(float* __restrict__ X, const float* __restrict__ y, const float
   const float4* yr = y ? reinterpret_cast<const float4*>(y + row * (size_t)W) : nullptr;
   float4 keep[HC_GROUPS];
   float ss = 0.f;
-  for (int g0 = 0; g0 < W4; g0 += HC_GROUPS * HC_THREADS) {
+  for (int g0 = 0; g0 < W4; g0 += HC_GROUPS * NT) {
     float4 old[HC_GROUPS][S], yv[HC_GROUPS];
 #pragma unroll
     for (int k = 0; k < HC_GROUPS; k++) {                 // every load of the pass is requested here
-      const int g = g0 + threadIdx.x + k * HC_THREADS;
+      const int g = g0 + threadIdx.x + k * NT;
       const bool live = g < W4;
       yv[k] = (yr && live) ? yr[g] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -150,7 +150,7 @@ k_hyper_connect4(float* __restrict__ X, const float* __restrict__ y, const float
     }
 #pragma unroll
     for (int k = 0; k < HC_GROUPS; k++) {
-      const int g = g0 + threadIdx.x + k * HC_THREADS;
+      const int g = g0 + threadIdx.x + k * NT;
       if (g >= W4) continue;
       float4 nw[S];
       if (yr && spread) {
@@ -184,12 +184,12 @@ k_hyper_connect4(float* __restrict__ X, const float* __restrict__ y, const float
   TH* hr = h + row * (size_t)W;
 #pragma unroll
   for (int k = 0; k < HC_GROUPS; k++) {
-    const int g = threadIdx.x + k * HC_THREADS;
+    const int g = threadIdx.x + k * NT;
     if (g >= W4) continue;
     const float4 u = keep[k];
     store4<TH>(hr + 4 * (size_t)g, make_float4(u.x * inv * wv[k].x, u.y * inv * wv[k].y, u.z * inv * wv[k].z, u.w * inv * wv[k].w));
   }
-  for (int g = HC_GROUPS * HC_THREADS + threadIdx.x; g < W4; g += HC_THREADS) {      // beyond the first pass: formed again, in the same order
+  for (int g = HC_GROUPS * NT + threadIdx.x; g < W4; g += NT) {      // beyond the first pass: formed again, in the same order
     float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int t = 0; t < S; t++) u = f4_fma(ra[t], xr[(size_t)t * W4 + g], u);
@@ -201,11 +201,12 @@ k_hyper_connect4(float* __restrict__ X, const float* __restrict__ y, const float
 template <typename TH>
 static int launch_hyper4(float* X, const float* y, const float* C, const float* b, float mult, int spread, const float* a, const float* w,
                          float eps, TH* h, int T, int S, int W, cudaStream_t stream) {
+  const dim3 HC_BLOCK((W >> 2) <= HC_GROUPS * 128 ? 128 : HC_THREADS);      // every thread's groups are live where that covers the row
   switch (S) {
-    case 1: return cima_launch(k_hyper_connect4<TH, 1>, dim3(T), dim3(HC_THREADS), (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
-    case 2: return cima_launch(k_hyper_connect4<TH, 2>, dim3(T), dim3(HC_THREADS), (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
-    case 3: return cima_launch(k_hyper_connect4<TH, 3>, dim3(T), dim3(HC_THREADS), (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
-    default: return cima_launch(k_hyper_connect4<TH, 4>, dim3(T), dim3(HC_THREADS), (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
+    case 1: return cima_launch(k_hyper_connect4<TH, 1>, dim3(T), HC_BLOCK, (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
+    case 2: return cima_launch(k_hyper_connect4<TH, 2>, dim3(T), HC_BLOCK, (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
+    case 3: return cima_launch(k_hyper_connect4<TH, 3>, dim3(T), HC_BLOCK, (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
+    default: return cima_launch(k_hyper_connect4<TH, 4>, dim3(T), HC_BLOCK, (size_t)0, stream, 1, X, y, C, b, mult, spread, a, w, eps, h, W);
   }
 }
 
