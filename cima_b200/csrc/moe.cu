@@ -253,6 +253,42 @@ k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const 
   }
 }
 
+// The same for rows whose width is a multiple of 4 and at most COMBINE_TOP choices: four columns a thread, the choices'
+// weights and places fetched once a row, and the rows of all choices requested before the first is used.  The sum runs
+// over j in the same ascending order.
+constexpr int COMBINE_TOP = 8;
+__global__ void __launch_bounds__(128)
+k_moe_combine4(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ pos, float* __restrict__ x,
+               int top, int H4, int assign, const float* __restrict__ shared, const float* __restrict__ gate, int ldg) {
+  cima_pdl_wait();
+  cima_pdl_trigger();
+  const size_t row = blockIdx.x;
+  float w[COMBINE_TOP];
+  const float4* src[COMBINE_TOP];
+#pragma unroll
+  for (int j = 0; j < COMBINE_TOP; j++) {
+    const size_t p = row * top + (j < top ? j : 0);
+    w[j] = j < top ? wgt[p] : 0.f;
+    src[j] = reinterpret_cast<const float4*>(y) + (pos ? (size_t)pos[p] : p) * H4;
+  }
+  const float sg = shared ? (gate ? 1.0f / (1.0f + expf(-gate[row * (size_t)ldg])) : 1.0f) : 0.f;
+  const float4* sh = shared ? reinterpret_cast<const float4*>(shared) + row * H4 : nullptr;
+  float4* xr = reinterpret_cast<float4*>(x) + row * H4;
+  for (int g = threadIdx.x; g < H4; g += blockDim.x) {
+    float4 v[COMBINE_TOP];
+#pragma unroll
+    for (int j = 0; j < COMBINE_TOP; j++) v[j] = j < top ? src[j][g] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 sv = sh ? sh[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 xo = assign ? make_float4(0.f, 0.f, 0.f, 0.f) : xr[g];
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < COMBINE_TOP; j++)
+      if (j < top) { s.x = fmaf(w[j], v[j].x, s.x); s.y = fmaf(w[j], v[j].y, s.y); s.z = fmaf(w[j], v[j].z, s.z); s.w = fmaf(w[j], v[j].w, s.w); }
+    if (sh) { s.x = fmaf(sg, sv.x, s.x); s.y = fmaf(sg, sv.y, s.y); s.z = fmaf(sg, sv.z, s.z); s.w = fmaf(sg, sv.w, s.w); }
+    xr[g] = assign ? s : make_float4(xo.x + s.x, xo.y + s.y, xo.z + s.z, xo.w + s.w);
+  }
+}
+
 // Every expert's pairs from a multiple of `tile` rows on: pos [P] the place of every pair, tile_expert [n_tiles] the
 // expert of every row tile (-1 beyond the last).  One block.
 __global__ void __launch_bounds__(1024)
@@ -451,6 +487,10 @@ extern "C" int cima_moe_gemm(const void* a, int adtype, int lda, const void* w, 
 extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos, float* x, int T, int top, int H, int assign,
                                 const float* shared, const float* gate, int ldg, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (top <= COMBINE_TOP && H % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)shared) & 15) == 0) {
+    int rc4 = cima_launch(k_moe_combine4, dim3(T), dim3(128), (size_t)0, stream, 1, y, wgt, pos, x, top, H / 4, assign, shared, gate, ldg);
+    return rc4 ? rc4 : cima_launch_result();
+  }
   int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H, assign, shared, gate, ldg);
   return rc ? rc : cima_launch_result();
 }
