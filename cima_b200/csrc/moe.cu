@@ -274,7 +274,8 @@ k_moe_combine4(const float* __restrict__ y, const float* __restrict__ wgt, const
   const float sg = shared ? (gate ? 1.0f / (1.0f + expf(-gate[row * (size_t)ldg])) : 1.0f) : 0.f;
   const float4* sh = shared ? reinterpret_cast<const float4*>(shared) + row * H4 : nullptr;
   float4* xr = reinterpret_cast<float4*>(x) + row * H4;
-  for (int g = threadIdx.x; g < H4; g += blockDim.x) {
+  // (a block takes 128 groups of four columns: a decode step's few rows are spread over many blocks)
+  for (int g = blockIdx.y * blockDim.x + threadIdx.x; g < H4; g += gridDim.y * blockDim.x) {
     float4 v[COMBINE_TOP];
 #pragma unroll
     for (int j = 0; j < COMBINE_TOP; j++) v[j] = j < top ? src[j][g] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -488,7 +489,8 @@ extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos
                                 const float* shared, const float* gate, int ldg, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top <= COMBINE_TOP && H % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)shared) & 15) == 0) {
-    int rc4 = cima_launch(k_moe_combine4, dim3(T), dim3(128), (size_t)0, stream, 1, y, wgt, pos, x, top, H / 4, assign, shared, gate, ldg);
+    const unsigned parts = (unsigned)((H / 4 + 127) / 128);
+    int rc4 = cima_launch(k_moe_combine4, dim3(T, parts > 65535 ? 65535 : parts), dim3(128), (size_t)0, stream, 1, y, wgt, pos, x, top, H / 4, assign, shared, gate, ldg);
     return rc4 ? rc4 : cima_launch_result();
   }
   int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H, assign, shared, gate, ldg);

@@ -82,7 +82,12 @@ class RoutedExperts:
         s, rt = self.spec, self.rt
         rows = [tensors[self._n(prefix, names, "router")]]
         if self.shared_gate:
+            # the gate's row under the router's, then zero rows up to a multiple of 8 outputs (a row of the scores keeps its
+            # 16-byte alignment, and the library's product of many rows its fast kernels)
             rows.append(tensors[self._n(prefix, names, "shared.sg")])
+            pad = -(self.E + 1) % 8
+            if pad:
+                rows.append(torch.zeros((pad, s.hidden), dtype=rows[0].dtype, device=rows[0].device))
         self.router = Linear(rows, None, rt)
         del rows
         if self.has_correction:
@@ -112,7 +117,7 @@ class RoutedExperts:
             out[self._n(prefix, names, "shared.gate")], out[self._n(prefix, names, "shared.up")] = w[:I], w[I:]
             out[self._n(prefix, names, "shared.down")] = self.shared_down.weight
             if self.shared_gate:
-                out[self._n(prefix, names, "shared.sg")] = self.router.weight[self.E:]
+                out[self._n(prefix, names, "shared.sg")] = self.router.weight[self.E:self.E + 1]
         for j in range(self.E):
             out[self._n(prefix, names, f"e{j}.gate")] = self.gate_up[j, :ff]
             out[self._n(prefix, names, f"e{j}.up")] = self.gate_up[j, ff:]
