@@ -27,9 +27,11 @@ def attention(heads, kv_heads, dim, vdim, scale, rot, mask, mlp):
     return {"type": "attention", "mixer": m, "mlp": mlp}
 
 
-def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, base, window, mlp):
+def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, base, window, mlp, scaling=None):
     m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale,
          "rot": {"dims": rot_dim, "base": base}}
+    if scaling is not None:
+        m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
     if window:
         m["mask"] = {"size": window}
     return {"type": "latent_attention", "mixer": m, "mlp": mlp}
@@ -63,11 +65,13 @@ N_A = config(300, 96, 1e-5, 0.5, 3, [
     latent(2, 24, 16, 16, 48, 24, 0.2, 300.0, 64, moe(5, 1, 24, 0.75))])
 # one stream that still has its stored connection; a width that is no multiple of 8; a multiplier of 1; one key head for
 # all; whole heads rotate, frequencies as they are; a window of one position with one kept position; a window no test
-# sequence reaches; one expert of one; a latent layer without a window
+# sequence reaches; one expert of one; a latent layer without a window whose key part rotates with rescaled frequencies; a
+# layer whose heads rotate whole and have keys and values of one size (a decode step's projection rotates and appends itself)
 N_B = config(513, 100, 1e-6, 1.0, 1, [
-    latent(5, 8, 4, 12, 20, 16, 0.3, 100.0, 0, moe(1, 1, 16, 2.0, (8, 3.0))),
+    latent(5, 8, 4, 12, 20, 16, 0.3, 100.0, 0, moe(1, 1, 16, 2.0, (8, 3.0)), scaling=(4.0, 32, 8.0, 1.0)),
     attention(3, 1, 16, 40, 0.25, (16, 500.0, None), (1, 1), dense(33)),
-    attention(6, 3, 8, 8, 0.35, (4, 50000.0, (2.0, 16, 4.0, 1.0)), (4096, 0), moe(7, 7, 8, 1.0))])
+    attention(6, 3, 8, 8, 0.35, (4, 50000.0, (2.0, 16, 4.0, 1.0)), (4096, 0), moe(7, 7, 8, 1.0)),
+    attention(4, 2, 16, 16, 0.3, (16, 1000.0, None), (50, 0), None)])
 # no streams at all (the plain pre-norm sum); heads of 64 and 128 values; kept positions that fill a page and more behind a
 # window of exactly a page; a position that keeps 128 values and one that keeps 104 (no multiple of 16)
 N_C = config(640, 256, 1e-5, 0.7, None, [

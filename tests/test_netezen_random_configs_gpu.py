@@ -1,5 +1,5 @@
 """Netezen configurations drawn at random (every size and constant that config.json gives, layer by layer, in any order of
-the two layer kinds and the three feed-forwards, with one to four streams or none) in cuttings drawn at random too (whole,
+the two layer kinds and the three feed-forwards, with one to six streams or none) in cuttings drawn at random too (whole,
 a tail one by one, pieces, unequal batches): in 32-bit against the plain implementation on weights that make attention
 sharp, and in bfloat16 against the 32-bit engine on milder weights of the same configuration."""
 import os
@@ -53,9 +53,10 @@ def draw_config(rng: random.Random) -> dict:
             rank, rot = rng.choice([8, 16, 24, 40, 48, 64, 96, 112]), rng.choice([2, 4, 8, 16, 32])
             layers.append(latent(rng.randint(1, 6), rng.choice([8, 16, 24, 32, 64, 96]), rot, rng.choice([8, 16, 24, 32, 64, 100]), rank,
                                  rng.choice([8, 16, 24, 48, 96]), rng.choice([0.08, 0.15, 0.3]), rng.choice([50.0, 10000.0, 200000.0]),
-                                 rng.choice([0] + WINDOWS), draw_mlp(rng)))
+                                 rng.choice([0] + WINDOWS), draw_mlp(rng),
+                                 scaling=(rng.choice([2.0, 8.0]), rng.choice([16, 256]), rng.choice([8.0, 32.0]), 1.0) if rng.random() < 0.3 else None))
     return config(rng.choice([129, 333, 512, 1001]), width, rng.choice([1e-6, 1e-5, 3e-4]), rng.choice([0.3, 0.5, 1.0, 1.4]),
-                  rng.choice([None, 1, 2, 2, 3, 4]), layers)
+                  rng.choice([None, 1, 2, 2, 3, 4, 6]), layers)
 
 
 @pytest.mark.parametrize("seed", SEEDS)
